@@ -37,5 +37,5 @@ P
 # ncu --set full of the tcgen05 prefill attention: one 2048-token request, 2 layers
 CMD="timeout 300 python bench.py --batch 1 --prompt-len 2048 --steps 1 --warmup 1 --settle-steps 0 --layers 2 --no-cpu --profile-steps 0 --ttft-runs 1"
 $CMD > $O/r2d_plain_pf.log 2>&1 && \
-ncu --set full --clock-control none --import-source on --kernel-name-base demangled -k regex:attn_prefill_tc -c 2 -f -o $O/prof_r2d_pf $CMD > $O/r2d_ncu_pf.log 2>&1
+ncu --set full --clock-control none --kernel-name-base demangled -k regex:attn_prefill_tc -c 2 -f -o $O/prof_r2d_pf $CMD > $O/r2d_ncu_pf.log 2>&1
 echo "ncu prefill attention rc=$?"; ls -la $O/prof_r2d_pf.ncu-rep

@@ -31,5 +31,5 @@ print(d["value"], d["ms_per_step"], "ttft", d["ttft_ms_p50"], d["ttft_single_ms_
 P
 CMD="timeout 300 python bench.py --batch 1 --prompt-len 2048 --steps 1 --warmup 1 --settle-steps 0 --layers 2 --no-cpu --profile-steps 0 --ttft-runs 1"
 $CMD > $O/r2g_plain_pf.log 2>&1 && \
-ncu --set full --clock-control none --import-source on --kernel-name-base demangled -k regex:attn_prefill_tc -c 2 -f -o $O/prof_r2g_pf $CMD > $O/r2g_ncu_pf.log 2>&1
+ncu --set full --clock-control none --kernel-name-base demangled -k regex:attn_prefill_tc -c 2 -f -o $O/prof_r2g_pf $CMD > $O/r2g_ncu_pf.log 2>&1
 echo "ncu rc=$?"
