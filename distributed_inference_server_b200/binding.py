@@ -34,6 +34,21 @@ class EngineConfig(C.Structure):
                 ("eos_token", C.c_int32), ("stream", C.c_void_p), ("nccl_id", C.c_uint8 * 128)]
 
 
+MIX_LIGHTNING, MIX_MINGRU, MIX_LATENT = range(3)
+MLP_NONE, MLP_DENSE, MLP_MOE = range(3)
+
+
+class LayerConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "dim", "vdim", "width", "kv_rank", "rot_dim", "rot_dims", "kv_from")] + \
+               [("rot_base", C.c_float), ("scale", C.c_float), ("decay", C.POINTER(C.c_float))] + \
+               [(n, C.c_int32) for n in ("mlp", "ff", "experts", "top")] + [("limit", C.c_float)]
+
+
+class StackConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("vocab", "width", "n_layers", "canon_taps", "max_ctx", "max_logit_rows", "compute_dtype")] + \
+               [("norm_eps", C.c_float), ("layers", C.POINTER(LayerConfig))]
+
+
 class SamplingParams(C.Structure):
     _fields_ = [("max_tokens", C.c_int32), ("temperature", C.c_float), ("top_p", C.c_float), ("seed", C.c_uint64),
                 ("stop_tokens", C.POINTER(C.c_uint32)), ("stop_lens", C.POINTER(C.c_int32)), ("n_stop", C.c_int32)]
@@ -79,6 +94,11 @@ PROTOTYPES = {
     "dis_abi_version": (C.c_int, []),
     "dis_build_id": (C.c_char_p, []),
     "dis_engine_create": (C.c_int, [C.POINTER(EngineConfig), C.POINTER(vp)]),
+    "dis_engine_create_stack": (C.c_int, [C.POINTER(EngineConfig), C.POINTER(StackConfig), C.POINTER(vp)]),
+    "dis_engine_load_named": (C.c_int, [vp, C.c_char_p, vp, C.c_int, vp, C.c_int32]),
+    "dis_engine_seq_extend": (C.c_int, [vp, C.c_int32, vp, C.c_int32, vp, C.c_int32]),
+    "dis_engine_seq_probe": (C.c_int, [vp, C.c_int32, vp, C.c_int32]),
+    "dis_engine_last_logit_rows": (C.c_int, [vp, i32p]),
     "dis_engine_destroy": (C.c_int, [vp]),
     "dis_last_error": (C.c_char_p, []),
     "dis_engine_last_error": (C.c_char_p, [vp]),

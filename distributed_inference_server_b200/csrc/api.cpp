@@ -33,6 +33,39 @@ int dis_engine_create(const dis_engine_config *cfg, dis_engine **out) {
   return DIS_OK;
 }
 
+int dis_engine_create_stack(const dis_engine_config *cfg, const dis_stack_config *stack, dis_engine **out) {
+  if (!cfg || !stack || !out) { dis::set_last_error("dis_engine_create_stack: null argument"); return DIS_ERR_INVALID_ARGUMENT; }
+  *out = nullptr;
+  dis_engine *e = new (std::nothrow) dis_engine();
+  if (!e) { dis::set_last_error("host allocation failed"); return DIS_ERR_OUT_OF_MEMORY; }
+  const int rc = e->eng.init_stack(cfg, stack);
+  if (rc != DIS_OK) { std::string msg = e->eng.last_error; delete e; dis::set_last_error(msg); return rc; }
+  *out = e;
+  return DIS_OK;
+}
+int dis_engine_load_named(dis_engine *e, const char *name, const void *host, int dtype, const int64_t *shape, int32_t ndim) {
+  if (int rc = guard_null(e)) return rc;
+  LOCKED(e);
+  return e->eng.load_named(name, host, dtype, shape, ndim);
+}
+int dis_engine_seq_extend(dis_engine *e, int32_t slot, const uint32_t *tokens, int32_t n, const int32_t *probe, int32_t n_probe) {
+  if (int rc = guard_null(e)) return rc;
+  LOCKED(e);
+  return e->eng.seq_extend(slot, tokens, n, probe, n_probe);
+}
+int dis_engine_seq_probe(dis_engine *e, int32_t slot, const int32_t *positions, int32_t n) {
+  if (int rc = guard_null(e)) return rc;
+  LOCKED(e);
+  return e->eng.seq_probe(slot, positions, n);
+}
+int dis_engine_last_logit_rows(dis_engine *e, int32_t *n_rows) {
+  if (int rc = guard_null(e)) return rc;
+  if (!n_rows) return DIS_ERR_INVALID_ARGUMENT;
+  LOCKED(e);
+  *n_rows = e->eng.last_rows;
+  return DIS_OK;
+}
+
 int dis_engine_destroy(dis_engine *e) {
   if (int rc = guard_null(e)) return rc;
   { LOCKED(e); e->eng.shut = true; }

@@ -340,6 +340,7 @@ int Engine::tp_import(const uint8_t *handles) {
 Engine::~Engine() {
   if (cfg.device >= 0) cudaSetDevice(cfg.device);
   if (stream) cudaStreamSynchronize(stream);
+  free_stack();
   for (auto &g : graphs) cudaGraphExecDestroy(g.second);
   for (auto ev : prof_events) cudaEventDestroy(ev);
   if (comm && nccl) nccl->CommDestroy(comm);
@@ -386,6 +387,7 @@ bool Engine::tensor_slot(int kind, int layer, TensorSlot *o) {
 
 int Engine::load_tensor(int kind, int layer, const void *host, int dtype) {
   if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
+  if (stack) return fail(DIS_ERR_INVALID_ARGUMENT, "load_tensor (tensors of this family are loaded by name): not available for a layer-list model");
   if (!host) return fail(DIS_ERR_INVALID_ARGUMENT, "load_tensor: null host pointer");
   if (dtype != DIS_F32 && dtype != DIS_BF16) return fail(DIS_ERR_INVALID_ARGUMENT, "load_tensor: dtype must be f32 or bf16");
   TensorSlot s;
@@ -430,6 +432,7 @@ static void synth_params(const dis_model_config &m, int kind, float *amp, float 
 
 int Engine::load_synthetic(uint64_t seed) {
   if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
+  if (stack) return fail(DIS_ERR_INVALID_ARGUMENT, "load_synthetic: not available for a layer-list model");
   ENG_CUDA(cudaSetDevice(cfg.device));
   uint16_t *tmp = nullptr;
   uint64_t dummy = 0;
@@ -460,6 +463,7 @@ int Engine::load_synthetic(uint64_t seed) {
 }
 
 int Engine::read_tensor(int kind, int layer, uint16_t *host, size_t *n) {
+  if (stack) return fail(DIS_ERR_INVALID_ARGUMENT, "read_tensor: not available for a layer-list model");
   TensorSlot s;
   if (!n || !tensor_slot(kind, layer, &s)) return fail(DIS_ERR_INVALID_ARGUMENT, "read_tensor: bad argument");
   const size_t need = s.rows * s.cols;
@@ -479,6 +483,9 @@ int Engine::read_tensor(int kind, int layer, uint16_t *host, size_t *n) {
 
 int Engine::finalize() {
   if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
+  if (stack)
+    for (auto &kv : stack_names)
+      if (!kv.second.loaded) return fail(DIS_ERR_MODEL_NOT_LOADED, "finalize: tensor '" + kv.first + "' was not loaded");
   loaded = true;
   return DIS_OK;
 }
@@ -524,7 +531,8 @@ int Engine::seq_add(const uint32_t *prompt, int n, const dis_sampling_params *p,
   if (hit) pt_dirty = true;
   s.cached = hit * page_size;
   s.prefill_pos = s.cached;
-  if (!ensure_pages(s, slot, n + 1)) { release_pages(s); return fail(DIS_ERR_OUT_OF_MEMORY, "seq_add: out of KV pages"); }
+  if (!ensure_pages(s, slot, stack ? n : n + 1)) {  // the layer-list family reserves the extra token when it decodes it
+  release_pages(s); return fail(DIS_ERR_OUT_OF_MEMORY, "seq_add: out of KV pages"); }
   s.used = true;
   s.prompt.assign(prompt, prompt + n);
   s.max_tokens = p->max_tokens;
@@ -827,6 +835,29 @@ cudaError_t Engine::gather_full_logits(int R) {
 int Engine::prefill(int n, const int *slots, uint32_t *out_tokens, int *out_finish) {
   if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
   if (!loaded) return fail(DIS_ERR_MODEL_NOT_LOADED, "model not loaded");
+  if (stack) {
+    // the layer-list family has one pass for everything: keep stepping until every listed prompt has been read
+    if (n <= 0 || n > max_batch || !slots || !out_tokens || !out_finish) return fail(DIS_ERR_INVALID_ARGUMENT, "prefill: bad argument");
+    for (int i = 0; i < n; i++)
+      if (slots[i] < 0 || slots[i] >= max_batch || !seqs[(size_t)slots[i]].used || seqs[(size_t)slots[i]].prefilled)
+        return fail(DIS_ERR_INVALID_ARGUMENT, "prefill: no such sequence, or already prefilled");
+    std::vector<int> todo(slots, slots + n), prod((size_t)n);
+    std::vector<uint32_t> tk((size_t)n);
+    std::vector<int> fin((size_t)n);
+    while (!todo.empty()) {
+      const int k = (int)todo.size();
+      const int rc = stack_step(k, todo.data(), 0, tk.data(), fin.data(), prod.data());
+      if (rc != DIS_OK) return rc;
+      std::vector<int> next;
+      for (int j = 0; j < k; j++) {
+        const int at = (int)(std::find(slots, slots + n, todo[(size_t)j]) - slots);
+        if (prod[(size_t)j] || fin[(size_t)j] != DIS_FINISH_NONE) { out_tokens[at] = tk[(size_t)j]; out_finish[at] = fin[(size_t)j]; }
+        else next.push_back(todo[(size_t)j]);
+      }
+      todo.swap(next);
+    }
+    return DIS_OK;
+  }
   if (n <= 0 || n > max_batch || !slots || !out_tokens || !out_finish) return fail(DIS_ERR_INVALID_ARGUMENT, "prefill: bad argument");
   const uint64_t stamp = ++call_stamp;  // a slot seen twice in one call carries this call's stamp already
   for (int i = 0; i < n; i++) {
@@ -941,6 +972,7 @@ void plan_mixed_step(int n, const int *remaining_prompt, int budget, int cap, in
 int Engine::step_mixed(int n, const int *slots, int max_prefill_tokens, uint32_t *out_tokens, int *out_finish, int *out_produced) {
   if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
   if (!loaded) return fail(DIS_ERR_MODEL_NOT_LOADED, "model not loaded");
+  if (stack) return stack_step(n, slots, max_prefill_tokens, out_tokens, out_finish, out_produced);
   if (n <= 0 || n > max_batch || !slots || !out_tokens || !out_finish || !out_produced) return fail(DIS_ERR_INVALID_ARGUMENT, "step: bad argument");
   const uint64_t stamp = ++call_stamp;
   for (int i = 0; i < n; i++) {
@@ -1058,6 +1090,14 @@ int Engine::step_mixed(int n, const int *slots, int max_prefill_tokens, uint32_t
 
 // ------------------------------------------------------------------------------------ decode
 int Engine::decode(int n, const int *slots, uint32_t *out_tokens, int *out_finish) {
+  if (stack && !shut && loaded) {
+    if (n <= 0 || n > max_batch || !slots || !out_tokens || !out_finish) return fail(DIS_ERR_INVALID_ARGUMENT, "decode: bad argument");
+    for (int i = 0; i < n; i++)
+      if (slots[i] < 0 || slots[i] >= max_batch || !seqs[(size_t)slots[i]].used || !seqs[(size_t)slots[i]].prefilled)
+        return fail(DIS_ERR_INVALID_ARGUMENT, "decode: sequence not prefilled");
+    std::vector<int> prod((size_t)n);
+    return stack_step(n, slots, 0, out_tokens, out_finish, prod.data());
+  }
   if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
   if (!loaded) return fail(DIS_ERR_MODEL_NOT_LOADED, "model not loaded");
   if (n <= 0 || n > max_batch || !slots || !out_tokens || !out_finish) return fail(DIS_ERR_INVALID_ARGUMENT, "decode: bad argument");
@@ -1199,6 +1239,7 @@ void Engine::prof_mark(int cls) {
 // summed device time per class (event to next event), class_launches how often each class ran.
 int Engine::profile_decode(int n, const int *slots, uint32_t *out_tokens, int *out_finish, float *class_ms,
                            int *class_launches) {
+  if (stack) return fail(DIS_ERR_INVALID_ARGUMENT, "profile_decode: not available for a layer-list model");
   if (!class_ms || !class_launches) return fail(DIS_ERR_INVALID_ARGUMENT, "profile_decode: null output");
   profiling = true;
   prof_marks.clear();
@@ -1218,7 +1259,9 @@ int Engine::profile_decode(int n, const int *slots, uint32_t *out_tokens, int *o
 int Engine::last_logits_host(float *host, int rows) {
   if (!host || rows <= 0 || rows > last_rows) return fail(DIS_ERR_INVALID_ARGUMENT, "last_logits: no such rows");
   ENG_CUDA(cudaSetDevice(cfg.device));
-  if (tp_size == 1) {
+  if (stack) {
+    ENG_CUDA(cudaMemcpyAsync(host, stack->logits, (size_t)rows * m.vocab * 4, cudaMemcpyDeviceToHost, stream));
+  } else if (tp_size == 1) {
     ENG_CUDA(cudaMemcpyAsync(host, logits, (size_t)rows * m.vocab * 4, cudaMemcpyDeviceToHost, stream));
   } else {
     ENG_CUDA(gather_full_logits(last_rows));

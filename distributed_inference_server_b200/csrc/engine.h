@@ -10,6 +10,7 @@
 #include "kernels.h"
 #include "prefix_index.hpp"
 #include "ptx.cuh"
+#include "stack.h"
 
 namespace dis {
 
@@ -45,6 +46,7 @@ struct Sequence {
   std::vector<std::vector<uint32_t>> stop;  // stop sequences
   std::vector<uint32_t> tail;               // last generated tokens, for stop matching
   std::vector<int> pages;
+  std::vector<int> probes;  // layer-list family: positions (ascending) whose logits the pass that reads them keeps
 };
 
 // Host-side image of the per-step device metadata (one pinned block, one H2D copy per step).
@@ -57,6 +59,7 @@ struct StepMeta {
   size_t o_tokens, o_pos, o_ptrow, o_ctx, o_rowmap, o_temp, o_topp, o_seed, o_step;
   size_t o_qb_tok0, o_qb_len, o_qb_pos0, o_qb_ptrow;  // prefill query blocks
   size_t o_arstep;                                     // forward-pass counter (epoch of the peer-memory exchange)
+  size_t o_span = 0, o_ab_tok0 = 0, o_ab_len = 0;       // layer-list family: span of each token; attention query blocks
   template <class T_> T_ *h(size_t off) { return reinterpret_cast<T_ *>(host + off); }
   template <class T_> T_ *d(size_t off) { return reinterpret_cast<T_ *>(dev + off); }
 };
@@ -155,6 +158,21 @@ struct Engine {
   int tp_export(uint8_t out[64]);
   int tp_import(const uint8_t *handles);
   cudaError_t consume_pending(const float *gain, const int *row_map, int rows, int T);
+
+  // layer-list decoders (stack.cu): the same sequences, pages, planner and sampler; prompt = the whole token history
+  StackModel *stack = nullptr;
+  std::vector<void *> stack_allocs;
+  struct StackTarget { StackTensor *dst; size_t off; std::vector<int64_t> shape; int transform; bool loaded; int layer; };
+  std::map<std::string, StackTarget> stack_names;
+  int stack_bq = 8;
+  int init_stack(const dis_engine_config *c, const dis_stack_config *sc);
+  int load_named(const char *name, const void *host, int dtype, const int64_t *shape, int ndim);
+  int stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t *out_tokens, int *out_finish, int *out_produced);
+  int seq_extend(int slot, const uint32_t *tokens, int n, const int *probe, int n_probe);
+  int seq_probe(int slot, const int *pos, int n);
+  cudaError_t stack_forward(int T, int n_spans, int n_qb, int R, bool all_greedy);
+  cudaError_t stack_meta(StepMeta &s, int cap_t, int cap_rows);
+  void free_stack();
 
   ~Engine();
   int fail(int code, const std::string &msg);

@@ -1,0 +1,330 @@
+// k_stack.cu -- kernels of the layer-list decoders (stack.h): a general fp32-accumulating matrix product over float or bf16
+// operands (plain, batched per head, or grouped per expert), the scalar-gain residual norms, the input convolution with its
+// per-slot tail, the two recurrences, latent attention over paged latents, the clamped gated unit and the expert router.
+// Everything the family defines as 32-bit -- norms, decays, recurrent state, scores and softmax, routers, the residual --
+// is fp32 here whatever the element type of the matrices.
+#include "stack_dev.cuh"
+
+namespace dis {
+
+// ------------------------------------------------------------------------------------------------ matrix product
+// out[m][n] = bias[n] + sum_k A[m][k] W[n][k].  64 x 64 tile per CTA, 16-deep slices through shared memory, 4 x 4 outputs per
+// thread, fp32 FMA: every output element is one k-ordered sum whatever tile it falls in, so a row's result does not depend on
+// the rows beside it.
+constexpr int GB = kStackGemmTile, GK = 16;
+
+template <bool AF32, bool WF32>
+__global__ void __launch_bounds__(256) stack_gemm_kernel(StackGemm g) {
+  __shared__ float As[GK][GB + 4], Ws[GK][GB + 4];
+  int row0, rows, grp = 0;
+  if (g.tiles) {
+    if ((int)blockIdx.x >= g.tiles[0]) return;
+    grp = g.tiles[1 + 3 * blockIdx.x];
+    row0 = g.tiles[2 + 3 * blockIdx.x];
+    rows = g.tiles[3 + 3 * blockIdx.x];
+  } else {
+    row0 = blockIdx.x * GB;
+    rows = min(GB, g.M - row0);
+  }
+  const int z = blockIdx.z;
+  const int n0 = blockIdx.y * GB;
+  const long long a_off = (long long)z * g.a_bs, w_off = (long long)z * g.w_bs + (long long)grp * (g.tiles ? g.w_bs : 0);
+  const float *bias = g.bias ? g.bias + (long long)z * g.bias_bs + (g.tiles ? (long long)grp * g.bias_bs : 0) : nullptr;
+  float *out = g.out + (long long)z * g.o_bs;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float acc[4][4] = {};
+  // loader: thread -> (row = tid / 4, k = (tid % 4) * 4 .. +3)
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  long long a_row = -1;
+  if (lr < rows) a_row = g.a_gather ? g.a_gather[row0 + lr] : row0 + lr;
+  const long long w_row = n0 + lr < g.N ? n0 + lr : -1;
+  for (int k0 = 0; k0 < g.K; k0 += GK) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int k = k0 + lk + j;
+      As[lk + j][lr] = (a_row >= 0 && k < g.K) ? ld_el<AF32>(g.A, a_off + a_row * g.lda + k) : 0.f;
+      Ws[lk + j][lr] = (w_row >= 0 && k < g.K) ? ld_el<WF32>(g.W, w_off + w_row * g.ldw + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GK; k++) {
+      const float4 a = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+      const float4 w = *reinterpret_cast<const float4 *>(&Ws[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n < g.N) out[(long long)(row0 + r) * g.ldo + n] = acc[i][j] + (bias ? bias[n] : 0.f);
+    }
+  }
+}
+
+cudaError_t launch_stack_gemm(const StackGemm &g, cudaStream_t st) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return cudaSuccess;
+  dim3 grid(g.tiles ? g.max_tiles : (g.M + GB - 1) / GB, (g.N + GB - 1) / GB, g.batch);
+  if (grid.x == 0) return cudaSuccess;
+  if (g.a_f32 && g.w_f32) stack_gemm_kernel<true, true><<<grid, 256, 0, st>>>(g);
+  else if (g.a_f32) stack_gemm_kernel<true, false><<<grid, 256, 0, st>>>(g);
+  else if (g.w_f32) stack_gemm_kernel<false, true><<<grid, 256, 0, st>>>(g);
+  else stack_gemm_kernel<false, false><<<grid, 256, 0, st>>>(g);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ embedding, norms
+template <bool F32>
+__global__ void stack_embed_kernel(const void *embed, const uint32_t *tokens, float *x, int W) {
+  const long long t = blockIdx.x;
+  const long long row = tokens[t];
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[t * W + i] = ld_el<F32>(embed, row * W + i);
+}
+cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, int T, int W, cudaStream_t st) {
+  if (f32) stack_embed_kernel<true><<<T, 128, 0, st>>>(embed, tokens, x, W);
+  else stack_embed_kernel<false><<<T, 128, 0, st>>>(embed, tokens, x, W);
+  return cudaGetLastError();
+}
+
+__global__ void __launch_bounds__(256) stack_resid_norm_kernel(float *x, const float *y, const float *post, const float *pre,
+                                                               float *hn, int W, float eps) {
+  __shared__ float sh[32];
+  const long long t = blockIdx.x;
+  float *xr = x + t * W;
+  if (y) {
+    const float *yr = y + t * W;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) s += yr[i] * yr[i];
+    s = block_sum(s, sh);
+    const float r = rsqrtf(s / (float)W + eps) * post[0];
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xr[i] += yr[i] * r;
+  }
+  if (!hn) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += xr[i] * xr[i];  // each thread re-reads what it wrote itself
+  s = block_sum(s, sh);
+  const float r = rsqrtf(s / (float)W + eps) * pre[0];
+  for (int i = threadIdx.x; i < W; i += blockDim.x) hn[t * W + i] = xr[i] * r;
+}
+cudaError_t launch_stack_resid_norm(float *x, const float *y, const float *post, const float *pre, float *hn, int T, int W,
+                                    float eps, cudaStream_t st) {
+  stack_resid_norm_kernel<<<T, 256, 0, st>>>(x, y, post, pre, hn, W, eps);
+  return cudaGetLastError();
+}
+
+template <bool F32>
+__global__ void stack_final_norm_kernel(const float *x, const int *row_map, const float *g, void *out, int W, float eps) {
+  __shared__ float sh[32];
+  const long long r = blockIdx.x;
+  const float *xr = x + (long long)(row_map ? row_map[r] : r) * W;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += xr[i] * xr[i];
+  s = block_sum(s, sh);
+  const float k = rsqrtf(s / (float)W + eps) * g[0];
+  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, xr[i] * k);
+}
+cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const float *g, void *out, bool f32, int R, int W, float eps,
+                                    cudaStream_t st) {
+  if (f32) stack_final_norm_kernel<true><<<R, 256, 0, st>>>(x, row_map, g, out, W, eps);
+  else stack_final_norm_kernel<false><<<R, 256, 0, st>>>(x, row_map, g, out, W, eps);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ input convolution
+// Input at absolute position p of the sequence: inside the span from hn, before it from the slot's tail (tail[i] holds position
+// pos0 - (taps-1) + i), before the sequence's start zero.  A span that starts at position 0 never reads the tail, so a slot
+// that another sequence used before needs no clearing.
+constexpr int kCanonMaxTaps = 16;
+
+template <bool F32>
+__global__ void stack_canon_kernel(const float *hn, const float *w, const float *state, StackSpans sp, void *hc, int W, int taps) {
+  const int t = blockIdx.x;
+  const int s = sp.span[t], tok0 = sp.sp_tok0[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  const int back_in_span = t - tok0;  // tokens of the span in front of t
+  const float *tail = state + (long long)slot * (taps - 1) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float cur = hn[(long long)t * W + i];
+    float acc = cur;
+    for (int j = 0; j < taps; j++) {
+      const int back = taps - 1 - j;
+      float v;
+      if (back <= back_in_span) v = hn[(long long)(t - back) * W + i];
+      else {
+        const int ti = (taps - 1) - (back - back_in_span);  // index into the tail
+        v = (pos0 + back_in_span - back >= 0) ? tail[(long long)ti * W + i] : 0.f;
+      }
+      acc = fmaf(w[(long long)i * taps + j], v, acc);
+    }
+    st_el<F32>(hc, (long long)t * W + i, acc);
+  }
+}
+
+__global__ void stack_canon_state_kernel(const float *hn, float *state, StackSpans sp, int W, int taps) {
+  const int s = blockIdx.x;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  float *tail = state + (long long)slot * (taps - 1) * W;
+  const int n = taps - 1;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float nv[kCanonMaxTaps];
+    for (int k = 0; k < n; k++) {
+      const int rel = len - n + k;  // index relative to the span's first token of the position tail'[k] holds
+      if (rel >= 0) nv[k] = hn[(long long)(tok0 + rel) * W + i];
+      else nv[k] = (pos0 + rel >= 0) ? tail[(long long)(n + rel) * W + i] : 0.f;
+    }
+    for (int k = 0; k < n; k++) tail[(long long)k * W + i] = nv[k];
+  }
+}
+
+cudaError_t launch_stack_canon(const float *hn, const float *w, float *state, const StackSpans &sp, void *hc, bool f32, int W,
+                               int taps, cudaStream_t st) {
+  if (taps < 1 || taps > kCanonMaxTaps) return cudaErrorInvalidValue;
+  if (f32) stack_canon_kernel<true><<<sp.T, 256, 0, st>>>(hn, w, state, sp, hc, W, taps);
+  else stack_canon_kernel<false><<<sp.T, 256, 0, st>>>(hn, w, state, sp, hc, W, taps);
+  if (taps > 1) stack_canon_state_kernel<<<sp.n_spans, 256, 0, st>>>(hn, state, sp, W, taps);
+  return cudaGetLastError();
+}
+
+template <bool F32>
+__global__ void stack_copy_act_kernel(const float *hn, void *hc, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    st_el<F32>(hc, i, hn[i]);
+}
+cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st) {
+  const int grid = (int)std::min<long long>((n + 255) / 256, 148 * 8);
+  if (f32) stack_copy_act_kernel<true><<<grid, 256, 0, st>>>(hn, hc, n);
+  else stack_copy_act_kernel<false><<<grid, 256, 0, st>>>(hn, hc, n);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ clamped gated unit
+template <bool F32>
+__global__ void stack_glu_kernel(const float *gu, void *act, const int *rows_ptr, int M, int ff, float limit) {
+  const long long rows = rows_ptr ? min(M, rows_ptr[0]) : M;
+  const long long n = rows * ff;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / ff, c = i % ff;
+    const float g = fminf(gu[r * 2 * ff + c], limit);
+    const float u = fminf(fmaxf(gu[r * 2 * ff + ff + c], -limit), limit);
+    st_el<F32>(act, i, g * sigmoid_precise(1.702f * g) * (u + 1.f));
+  }
+}
+cudaError_t launch_stack_glu(const float *gu, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit, cudaStream_t st) {
+  if (M <= 0) return cudaSuccess;
+  const int grid = (int)std::min<long long>(((long long)M * ff + 255) / 256, 148 * 8);
+  if (f32) stack_glu_kernel<true><<<grid, 256, 0, st>>>(gu, act, rows_ptr, M, ff, limit);
+  else stack_glu_kernel<false><<<grid, 256, 0, st>>>(gu, act, rows_ptr, M, ff, limit);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ router and expert rows
+// One warp per token: fp32 logits against the fp32 router matrix, then `top` rounds of arg-max (lowest index wins a tie), then
+// the softmax over the chosen logits.  E <= 1024 (logits sit in shared memory).
+template <bool F32>
+__global__ void stack_route_kernel(const void *hc, const float *router, int T, int W, int E, int top, int *idx, float *wt) {
+  extern __shared__ float zs[];  // [warps][E]
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + w;
+  if (t >= T) return;
+  float *z = zs + (long long)w * E;
+  for (int e = 0; e < E; e++) {
+    float s = 0.f;
+    for (int i = l; i < W; i += 32) s = fmaf(ld_el<F32>(hc, (long long)t * W + i), router[(long long)e * W + i], s);
+    s = warp_sum(s);
+    if (l == 0) z[e] = s;
+  }
+  __syncwarp();
+  float m0 = 0.f, den = 0.f, mine = 0.f;
+  for (int k = 0; k < top; k++) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = l; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (k == 0) m0 = best;
+    const float p = expf(best - m0);
+    den += p;
+    if (l == k % 32) mine = p;  // lane k keeps the k-th weight (top <= 32)
+    if (l == 0) { idx[(long long)t * top + k] = bi; z[bi] = -INFINITY; }
+    __syncwarp();
+  }
+  if (l < top) wt[(long long)t * top + l] = mine / den;
+}
+cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
+                               cudaStream_t st) {
+  if (E > 1024 || top > 32 || top > E) return cudaErrorInvalidValue;
+  const int warps = 4;
+  const size_t sh = (size_t)warps * E * sizeof(float);
+  const int grid = (T + warps - 1) / warps;
+  if (f32) stack_route_kernel<true><<<grid, warps * 32, sh, st>>>(hc, router, T, W, E, top, idx, wt);
+  else stack_route_kernel<false><<<grid, warps * 32, sh, st>>>(hc, router, T, W, E, top, idx, wt);
+  return cudaGetLastError();
+}
+
+// Rows of the experts' matrices: the (token, choice) pairs sorted by expert, every expert's rows padded to whole row tiles in
+// the tile list only (the row space itself is dense).  One block; tokens are walked in order, so a pair's row is a function of
+// the routing alone.
+__global__ void stack_moe_plan_kernel(const int *idx, int n, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
+                                      int *tiles, int max_tiles) {
+  extern __shared__ int sh[];  // [E] counts, [E] offsets
+  int *cnt = sh, *off = sh + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, nt = 0;
+    for (int e = 0; e < E; e++) {
+      off[e] = o;
+      for (int r = 0; r < cnt[e] && nt < max_tiles; r += tile_rows) {
+        tiles[1 + 3 * nt] = e; tiles[2 + 3 * nt] = o + r; tiles[3 + 3 * nt] = min(tile_rows, cnt[e] - r);
+        nt++;
+      }
+      o += cnt[e];
+      counts[e] = cnt[e];
+    }
+    tiles[0] = nt;
+  }
+  __syncthreads();
+  // one thread per expert walks the pairs in order: stable, no atomics on the positions
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int o = off[e];
+    for (int i = 0; i < n; i++)
+      if (idx[i] == e) { perm_tok[o] = i / top; where[i] = o; o++; }
+  }
+}
+cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
+                                  int *tiles, int max_tiles, cudaStream_t st) {
+  stack_moe_plan_kernel<<<1, 256, (size_t)2 * E * sizeof(int), st>>>(idx, T * top, top, E, tile_rows, counts, perm_tok, where, tiles,
+                                                                      max_tiles);
+  return cudaGetLastError();
+}
+
+__global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, float *y, int W, int top) {
+  const long long t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < top; k++) s = fmaf(wt[t * top + k], rows[(long long)where[t * top + k] * W + i], s);
+    y[t * W + i] = s;
+  }
+}
+cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, float *y, int T, int W, int top,
+                                     cudaStream_t st) {
+  stack_moe_combine_kernel<<<T, 256, 0, st>>>(rows, where, wt, y, W, top);
+  return cudaGetLastError();
+}
+
+}  // namespace dis

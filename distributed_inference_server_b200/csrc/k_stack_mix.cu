@@ -1,0 +1,269 @@
+// k_stack_mix.cu -- the token mixers of the layer-list decoders: the decayed linear-attention scan, the minimal gated recurrence,
+// and latent attention (query absorption happens in a batched matrix product in stack.cu; here: rotary + cache write, and the
+// attention itself over the paged latents).  States and scores are fp32.
+#include "stack_dev.cuh"
+
+namespace dis {
+
+__device__ __forceinline__ float silu_(float v) { return v / (1.f + expf(-v)); }
+
+// ------------------------------------------------------------------------------------------------ linear attention
+// One CTA per (span, head).  S [d][dv] lives in shared memory for the whole span; per token: S = a S + k v^T, o = S^T q.
+// Warp w owns rows i = w, w + nw, ...; lanes own columns.  The partial o of every warp goes through shared memory and is added
+// in warp order, so the sum's order is fixed.  A span that starts at position 0 starts from S = 0 (the slot is not read).
+__global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj, long long ld, const float *decay, float *state,
+                                                              StackSpans sp, float *o, int H, int d, int dv) {
+  extern __shared__ float shm[];
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  float *S = shm;                 // [d][dv]
+  float *qs = S + (size_t)d * dv; // [d]
+  float *ks = qs + d;             // [d]
+  float *vs = ks + d;             // [dv]
+  float *part = vs + dv;          // [nw][dv]
+  float *st = state + ((long long)slot * H + h) * d * dv;
+  const float a = decay[h];
+  for (int i = threadIdx.x; i < d * dv; i += blockDim.x) S[i] = pos0 > 0 ? st[i] : 0.f;
+  for (int t = 0; t < len; t++) {
+    const float *row = proj + (long long)(tok0 + t) * ld;
+    __syncthreads();
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      qs[i] = silu_(row[(long long)h * d + i]);
+      ks[i] = silu_(row[(long long)H * d + (long long)h * d + i]);
+    }
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) vs[j] = silu_(row[(long long)2 * H * d + (long long)h * dv + j]);
+    __syncthreads();
+    for (int j = l; j < dv; j += 32) {
+      const float vj = vs[j];
+      float acc = 0.f;
+      for (int i = w; i < d; i += nw) {
+        const float sv = fmaf(a, S[(size_t)i * dv + j], ks[i] * vj);
+        S[(size_t)i * dv + j] = sv;
+        acc = fmaf(sv, qs[i], acc);
+      }
+      part[(size_t)w * dv + j] = acc;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < nw; k++) acc += part[(size_t)k * dv + j];
+      o[(long long)(tok0 + t) * H * dv + (long long)h * dv + j] = acc;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d * dv; i += blockDim.x) st[i] = S[i];
+}
+
+cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
+                                   float *o, int H, int d, int dv, cudaStream_t st) {
+  const int threads = 256;
+  const size_t sh = ((size_t)d * dv + 2 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
+  if (sh > 220 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
+  stack_lightning_kernel<<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
+  return cudaGetLastError();
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(256) stack_norm_gate_kernel(const float *o, const float *w, const float *gate, long long ldg,
+                                                              void *out, int n, float eps) {
+  __shared__ float sh[32];
+  const long long t = blockIdx.x;
+  const float *r = o + t * n;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += r[i] * r[i];
+  s = block_sum(s, sh);
+  const float k = rsqrtf(s / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    st_el<F32>(out, t * n + i, r[i] * k * w[i] * sigmoid_precise(gate[t * ldg + i]));
+}
+cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *gate, long long ldg, void *out, bool f32, int T,
+                                   int n, float eps, cudaStream_t st) {
+  if (f32) stack_norm_gate_kernel<true><<<T, 256, 0, st>>>(o, w, gate, ldg, out, n, eps);
+  else stack_norm_gate_kernel<false><<<T, 256, 0, st>>>(o, w, gate, ldg, out, n, eps);
+  return cudaGetLastError();
+}
+
+template <bool F32>
+__global__ void stack_gate_kernel(const float *o, const float *gate, long long ldg, void *out, int T, int n) {
+  const long long tot = (long long)T * n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < tot; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / n, c = i % n;
+    st_el<F32>(out, i, o[i] * sigmoid_precise(gate[t * ldg + c]));
+  }
+}
+cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, void *out, bool f32, int T, int n, cudaStream_t st) {
+  const int grid = (int)std::min<long long>(((long long)T * n + 255) / 256, 148 * 8);
+  if (f32) stack_gate_kernel<true><<<grid, 256, 0, st>>>(o, gate, ldg, out, T, n);
+  else stack_gate_kernel<false><<<grid, 256, 0, st>>>(o, gate, ldg, out, T, n);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ minimal gated recurrence
+// One thread per channel walks the span: z = sigmoid(pz), c = pu + 1/2 (pu >= 0) or sigmoid(pu), S = (1 - z) S + z c.
+template <bool F32>
+__global__ void stack_mingru_kernel(const float *proj, long long ld, float *state, StackSpans sp, void *out, int n) {
+  const int s = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  float S = pos0 > 0 ? state[(long long)slot * n + i] : 0.f;
+  for (int t = 0; t < len; t++) {
+    const float *row = proj + (long long)(tok0 + t) * ld;
+    const float z = sigmoid_precise(row[i]);
+    const float u = row[n + i];
+    const float c = u >= 0.f ? u + 0.5f : sigmoid_precise(u);
+    S = (1.f - z) * S + z * c;
+    st_el<F32>(out, (long long)(tok0 + t) * n + i, S * silu_(row[2 * (long long)n + i]));
+  }
+  state[(long long)slot * n + i] = S;
+}
+cudaError_t launch_stack_mingru(const float *proj, long long ld, float *state, const StackSpans &sp, void *out, bool f32, int n,
+                                cudaStream_t st) {
+  dim3 grid(sp.n_spans, (n + 127) / 128);
+  if (f32) stack_mingru_kernel<true><<<grid, 128, 0, st>>>(proj, ld, state, sp, out, n);
+  else stack_mingru_kernel<false><<<grid, 128, 0, st>>>(proj, ld, state, sp, out, n);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ latent attention
+// Rotation of coordinates (i, i + rot_dims/2), i < rot_dims/2, by the angle pos * base^(-2i/rot_dims); the rest passes.  The angle
+// is formed in double so that position 5000 is as exact as position 5.
+__device__ __forceinline__ float rotated(const float *v, int i, int rot_dims, int pos, float base) {
+  const int half = rot_dims >> 1;
+  if (i >= rot_dims) return v[i];
+  const int p = i < half ? i : i - half;
+  const double f = exp2(-2.0 * (double)p / (double)rot_dims * log2((double)base));
+  double sn, cs;
+  sincos((double)pos * f, &sn, &cs);
+  return i < half ? (float)((double)v[i] * cs - (double)v[i + half] * sn) : (float)((double)v[i] * cs + (double)v[i - half] * sn);
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(128) stack_latent_prep_kernel(const float *proj, long long ld, int q_off, int dkv_off,
+                                                                const float *dkv_norm, StackLatent c, StackSpans sp, float *qf,
+                                                                void *pool, const int *page_table, int max_pages, int page_size) {
+  __shared__ float sh[32];
+  const int t = blockIdx.x;
+  const float *row = proj + (long long)t * ld;
+  const int pos = sp.pos[t];
+  const int D = c.r + c.dr;
+  for (int i = threadIdx.x; i < c.H * c.dr; i += blockDim.x) {
+    const int h = i / c.dr, k = i % c.dr;
+    qf[((long long)t * c.H + h) * D + c.r + k] = rotated(row + q_off + (long long)h * (c.d + c.dr) + c.d, k, c.rot_dims, pos, c.rot_base);
+  }
+  if (!pool) return;
+  const int slot = sp.slot[t];
+  const long long prow = (long long)page_table[(long long)slot * max_pages + pos / page_size] * page_size + pos % page_size;
+  const float *dk = row + dkv_off;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < c.r; i += blockDim.x) s += dk[i] * dk[i];
+  s = block_sum(s, sh);
+  const float k = rsqrtf(s / (float)c.r + c.eps);
+  for (int i = threadIdx.x; i < c.r; i += blockDim.x) st_el<F32>(pool, prow * D + i, dk[i] * k * dkv_norm[i]);
+  for (int i = threadIdx.x; i < c.dr; i += blockDim.x) st_el<F32>(pool, prow * D + c.r + i, rotated(dk + c.r, i, c.rot_dims, pos, c.rot_base));
+}
+cudaError_t launch_stack_latent_prep(const float *proj, long long ld, int q_off, int dkv_off, const float *dkv_norm,
+                                     const StackLatent &c, const StackSpans &sp, float *qf, void *pool, bool f32,
+                                     const int *page_table, int max_pages, int page_size, cudaStream_t st) {
+  if (f32) stack_latent_prep_kernel<true><<<sp.T, 128, 0, st>>>(proj, ld, q_off, dkv_off, dkv_norm, c, sp, qf, pool, page_table, max_pages, page_size);
+  else stack_latent_prep_kernel<false><<<sp.T, 128, 0, st>>>(proj, ld, q_off, dkv_off, dkv_norm, c, sp, qf, pool, page_table, max_pages, page_size);
+  return cudaGetLastError();
+}
+
+// One CTA per query block (tokens of one span) over all heads: 32-key tiles of the sequence's pool rows are staged in shared
+// memory as fp32 and shared by every (token, head) pair of the block; one warp per pair at a time: a lane scores one key of the
+// tile against the pair's query (latent part absorbed into the query, rotated part appended), the warp keeps a running maximum
+// that starts at the head's sink and a running denominator that starts at exp(sink - max) = 1, and lanes own coordinates of
+// the output latent.  Per-pair running state lives in shared memory between tiles.
+constexpr int kLatTile = 32, kLatWarps = 8, kLatMaxR = 1024;
+
+int stack_latent_block_tokens(const StackLatent &c) {
+  // shared memory: tile [32][D+1] + per pair (D query + r accumulators + 2)
+  const int D = c.r + c.dr;
+  int bq = 8;
+  while (bq > 1 && ((size_t)kLatTile * (D + 1) + (size_t)bq * c.H * (D + c.r + 2)) * 4 > 200 * 1024) bq >>= 1;
+  return bq;
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const float *qf, const void *pool, const float *sink,
+                                                                           StackLatent c, StackSpans sp, const int *qb_tok0,
+                                                                           const int *qb_len, const int *page_table, int max_pages,
+                                                                           int page_size, float *ol) {
+  extern __shared__ float shm[];
+  const int D = c.r + c.dr, DP = D + 1, r = c.r;
+  const int tok0 = qb_tok0[blockIdx.x], nq = qb_len[blockIdx.x];
+  const int pairs = nq * c.H;
+  float *tile = shm;                                // [32][DP]
+  float *qs = tile + (size_t)kLatTile * DP;        // [pairs][D]
+  float *acc = qs + (size_t)pairs * D;             // [pairs][r]
+  float *mx = acc + (size_t)pairs * r;             // [pairs]
+  float *dn = mx + pairs;                          // [pairs]
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const int slot = sp.slot[tok0];
+  const int last_pos = sp.pos[tok0 + nq - 1];
+  for (int i = threadIdx.x; i < pairs * D; i += blockDim.x) qs[i] = qf[(long long)tok0 * c.H * D + i];
+  for (int i = threadIdx.x; i < pairs * r; i += blockDim.x) acc[i] = 0.f;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) { mx[i] = sink[i % c.H]; dn[i] = 1.f; }
+  const int *pt = page_table + (long long)slot * max_pages;
+  for (int k0 = 0; k0 <= last_pos; k0 += kLatTile) {
+    const int nk = min(kLatTile, last_pos + 1 - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nk * D; i += blockDim.x) {
+      const int kk = i / D, cc = i % D, kp = k0 + kk;
+      const long long prow = (long long)pt[kp / page_size] * page_size + kp % page_size;
+      tile[(size_t)kk * DP + cc] = ld_el<F32>(pool, prow * D + cc);
+    }
+    __syncthreads();
+    for (int p = w; p < pairs; p += kLatWarps) {
+      const int qpos = sp.pos[tok0 + p / c.H];
+      const float *q = qs + (size_t)p * D;
+      float sc = -INFINITY;
+      if (l < nk && k0 + l <= qpos) {
+        const float *kr = tile + (size_t)l * DP;
+        float s = 0.f;
+        for (int i = 0; i < D; i++) s = fmaf(q[i], kr[i], s);
+        sc = s * c.scale;
+      }
+      const float m_old = mx[p];
+      const float m_new = fmaxf(m_old, warp_max(sc));
+      const float pr = sc == -INFINITY ? 0.f : expf(sc - m_new);
+      const float corr = expf(m_old - m_new);
+      const float psum = warp_sum(pr);
+      float *a = acc + (size_t)p * r;
+      for (int j = l; j < r; j += 32) {
+        float v = a[j] * corr;
+        for (int kk = 0; kk < nk; kk++) v = fmaf(__shfl_sync(0xffffffffu, pr, kk), tile[(size_t)kk * DP + j], v);
+        a[j] = v;
+      }
+      __syncwarp();
+      if (l == 0) { mx[p] = m_new; dn[p] = dn[p] * corr + psum; }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs * r; i += blockDim.x) ol[(long long)tok0 * c.H * r + i] = acc[i] / dn[i / r];
+}
+
+cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32, const float *sink, const StackLatent &c,
+                                     const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, const int *page_table,
+                                     int max_pages, int page_size, float *ol, cudaStream_t st) {
+  if (n_qb <= 0) return cudaSuccess;
+  if (c.r > kLatMaxR) return cudaErrorInvalidValue;
+  const int D = c.r + c.dr, bq = stack_latent_block_tokens(c);
+  const size_t sh = ((size_t)kLatTile * (D + 1) + (size_t)bq * c.H * (D + c.r + 2)) * sizeof(float);
+  if (sh > 220 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_latent_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_latent_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  }));
+  if (f32) stack_latent_attn_kernel<true><<<n_qb, kLatWarps * 32, sh, st>>>(qf, pool, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol);
+  else stack_latent_attn_kernel<false><<<n_qb, kLatWarps * 32, sh, st>>>(qf, pool, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol);
+  return cudaGetLastError();
+}
+
+}  // namespace dis

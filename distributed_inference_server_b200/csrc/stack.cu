@@ -1,0 +1,679 @@
+// stack.cu -- the layer-list decoder family inside the engine: configuration checks, allocation of weights / recurrent state /
+// latent page pools, loading tensors by name, and the one forward pass (prompt chunks and decode rows together) that
+// dis_engine_step, _prefill and _decode run for this family.  Sequences, page allocation, the step planner, the sampler,
+// the serving loop and the C ABI are the engine's own (engine.cu, serving.cpp); the reference has no such family.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+#include "engine.h"
+
+namespace dis {
+
+#define ENG_CUDA(expr)                                                                                \
+  do {                                                                                                \
+    cudaError_t _e = (expr);                                                                          \
+    if (_e != cudaSuccess) {                                                                          \
+      healthy = false;                                                                                \
+      const char *_g = get_last_error();                                                              \
+      std::string _m = (_g && *_g) ? std::string(_g) : std::string(cudaGetErrorString(_e));           \
+      return fail(_e == cudaErrorMemoryAllocation ? DIS_ERR_OUT_OF_MEMORY : DIS_ERR_INFERENCE_FAILED, \
+                  std::string(#expr) + ": " + _m);                                                    \
+    }                                                                                                 \
+  } while (0)
+#define RET_CUDA(expr)                \
+  do {                                \
+    cudaError_t _e = (expr);          \
+    if (_e != cudaSuccess) return _e; \
+  } while (0)
+
+static size_t align_up16(size_t v) { return (v + 15) / 16 * 16; }
+
+void Engine::free_stack() {
+  for (void *p : stack_allocs) cudaFree(p);
+  stack_allocs.clear();
+  if (stack) {
+    if (stack->h_out) cudaFreeHost(stack->h_out);
+    for (StackTensor *v : stack->views) delete v;
+    delete stack;
+    stack = nullptr;
+  }
+}
+
+cudaError_t Engine::stack_meta(StepMeta &s, int cap_t, int cap_rows) {
+  s.cap_tokens = cap_t;
+  s.cap_rows = cap_rows;
+  size_t o = 0;
+  auto sec = [&](size_t bytes) { size_t at = o; o = align_up16(o + bytes); return at; };
+  const size_t ct = (size_t)cap_t, cr = (size_t)cap_rows;
+  s.o_tokens = sec(ct * 4); s.o_pos = sec(ct * 4); s.o_ptrow = sec(ct * 4); s.o_ctx = sec(ct * 4); s.o_span = sec(ct * 4);
+  s.o_rowmap = sec(cr * 4); s.o_temp = sec(cr * 4); s.o_topp = sec(cr * 4); s.o_seed = sec(cr * 8); s.o_step = sec(cr * 8);
+  s.o_qb_tok0 = sec(ct * 4); s.o_qb_len = sec(ct * 4); s.o_qb_pos0 = sec(ct * 4); s.o_qb_ptrow = sec(ct * 4);
+  s.o_ab_tok0 = sec(ct * 4); s.o_ab_len = sec(ct * 4);
+  s.o_arstep = sec(16);
+  s.bytes = o;
+  cudaError_t e = cudaMallocHost(reinterpret_cast<void **>(&s.host), s.bytes);
+  if (e != cudaSuccess) return e;
+  memset(s.host, 0, s.bytes);
+  e = cudaMalloc(reinterpret_cast<void **>(&s.dev), s.bytes);
+  if (e == cudaSuccess) bytes_allocated += s.bytes;
+  return e;
+}
+
+int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
+  cfg = *c;
+  if (!sc || !sc->layers || sc->n_layers <= 0 || sc->vocab <= 0 || sc->width <= 0 || sc->max_ctx <= 0)
+    return fail(DIS_ERR_INVALID_ARGUMENT, "stack config: vocab, width, layers and max_ctx must be positive");
+  if (c->tp_size > 1) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: tensor parallelism is not available for this family");
+  if (c->flags & DIS_FLAG_PREFIX_CACHE)
+    return fail(DIS_ERR_INVALID_ARGUMENT, "stack: the prefix cache cannot serve a family with recurrent state (a page does not hold it)");
+  if (sc->compute_dtype != DIS_F32 && sc->compute_dtype != DIS_BF16) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: compute_dtype");
+  if (sc->canon_taps < 0 || sc->canon_taps > 16) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: canon_taps must be 0..16");
+  memset(&m, 0, sizeof(m));
+  m.vocab = sc->vocab; m.hidden = sc->width; m.layers = sc->n_layers; m.max_ctx = sc->max_ctx; m.rms_eps = sc->norm_eps;
+  tp_rank = 0; tp_size = 1;
+  vocab_l = m.vocab; vocab_off = 0;
+  max_batch = c->max_batch > 0 ? c->max_batch : 32;
+  cap_tokens = std::max(c->max_step_tokens > 0 ? c->max_step_tokens : 8192, max_batch);
+  page_size = c->page_size > 0 ? c->page_size : 64;
+  if ((page_size & (page_size - 1)) || page_size < 8) return fail(DIS_ERR_INVALID_ARGUMENT, "page_size must be a power of two >= 8");
+  max_pages = (m.max_ctx + page_size - 1) / page_size;
+
+  stack = new StackModel();
+  StackModel &M = *stack;
+  M.c = *sc;
+  M.f32 = sc->compute_dtype == DIS_F32;
+  M.max_rows = std::max(sc->max_logit_rows > 0 ? sc->max_logit_rows : max_batch, max_batch);
+  M.layers.resize((size_t)sc->n_layers);
+  const int W = sc->width, taps = sc->canon_taps;
+  // ---- configuration checks, per layer
+  bool any_latent = false;
+  for (int i = 0; i < sc->n_layers; i++) {
+    StackLayer &L = M.layers[(size_t)i];
+    L.c = sc->layers[i];
+    const dis_layer_config &lc = L.c;
+    const std::string at = "stack layer " + std::to_string(i) + ": ";
+    if (lc.mixer == DIS_MIX_LIGHTNING) {
+      if (lc.heads <= 0 || lc.dim <= 0 || lc.vdim <= 0 || !lc.decay) return fail(DIS_ERR_INVALID_ARGUMENT, at + "lightning needs heads, dim, vdim, decay");
+      L.decay.assign(lc.decay, lc.decay + lc.heads);
+      L.c.decay = nullptr;
+      if (((size_t)lc.dim * lc.vdim + 2 * lc.dim + 9 * lc.vdim) * 4 > 220 * 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "dim * vdim does not fit shared memory");
+      L.n_in = 2 * lc.heads * lc.dim + 2 * lc.heads * lc.vdim;
+      L.g_off = 2 * lc.heads * lc.dim + lc.heads * lc.vdim;
+    } else if (lc.mixer == DIS_MIX_MINGRU) {
+      if (lc.width <= 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "mingru needs width");
+      L.n_in = 3 * lc.width;
+    } else if (lc.mixer == DIS_MIX_LATENT) {
+      if (lc.heads <= 0 || lc.dim <= 0 || lc.vdim <= 0 || lc.kv_rank <= 0 || lc.rot_dim < 0 || lc.rot_dims < 0 || lc.rot_dims > lc.rot_dim || (lc.rot_dims & 1))
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "latent attention needs heads, dim, vdim, kv_rank, and an even rot_dims <= rot_dim");
+      if (lc.kv_rank > 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_rank above 1024");
+      any_latent = true;
+      if (lc.kv_from >= 0) {
+        if (lc.kv_from >= i) return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name an earlier layer");
+        const dis_layer_config &src = M.layers[(size_t)lc.kv_from].c;
+        if (src.mixer != DIS_MIX_LATENT || src.kv_from >= 0 || src.kv_rank != lc.kv_rank || src.rot_dim != lc.rot_dim)
+          return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name a latent layer with a cache of its own and the same kv_rank and rot_dim");
+        L.kv_layer = lc.kv_from;
+      } else L.kv_layer = i;
+      L.q_off = 0;
+      L.dkv_off = lc.heads * (lc.dim + lc.rot_dim);
+      L.g_off = L.dkv_off + (lc.kv_from < 0 ? lc.kv_rank + lc.rot_dim : 0);
+      L.n_in = L.g_off + lc.heads * lc.vdim;
+      StackLatent sl{lc.heads, lc.dim, lc.rot_dim, lc.vdim, lc.kv_rank, lc.rot_dims, lc.rot_base, lc.scale, sc->norm_eps};
+      if (((size_t)32 * (lc.kv_rank + lc.rot_dim + 1) + (size_t)lc.heads * (2 * lc.kv_rank + lc.rot_dim + 2)) * 4 > 200 * 1024)
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "heads * kv_rank does not fit shared memory");
+      stack_bq = std::min(stack_bq, stack_latent_block_tokens(sl));
+    } else return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown mixer");
+    if (lc.mlp == DIS_MLP_DENSE) { if (lc.ff <= 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "ff"); }
+    else if (lc.mlp == DIS_MLP_MOE) {
+      if (lc.ff <= 0 || lc.experts <= 0 || lc.top <= 0 || lc.top > lc.experts || lc.top > 32 || lc.experts > 1024)
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "experts: 1 <= top <= min(experts, 32), experts <= 1024");
+    } else if (lc.mlp != DIS_MLP_NONE) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward kind");
+  }
+
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return fail(DIS_ERR_INFERENCE_FAILED, "no CUDA device: this engine has no CPU fallback");
+  if (c->device < 0 || c->device >= ndev) return fail(DIS_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+  ENG_CUDA(cudaSetDevice(c->device));
+  cudaDeviceProp prop;
+  ENG_CUDA(cudaGetDeviceProperties(&prop, c->device));
+  if (prop.major != 10) return fail(DIS_ERR_INFERENCE_FAILED, "device is not sm_100; kernels are built for sm_100a only");
+  if (c->stream) stream = (cudaStream_t)c->stream;
+  else { ENG_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking)); own_stream = true; }
+  ENG_CUDA(cudaEventCreate(&ev0));
+  ENG_CUDA(cudaEventCreate(&ev1));
+
+  const size_t esz = M.f32 ? 4 : 2;
+  auto alloc = [&](void **p, size_t bytes) -> cudaError_t {
+    *p = nullptr;
+    if (!bytes) return cudaSuccess;
+    cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) { set_last_error("cudaMalloc of " + std::to_string(bytes) + " bytes failed"); return e; }
+    stack_allocs.push_back(*p);
+    bytes_allocated += bytes;
+    return cudaMemset(*p, 0, bytes);
+  };
+  auto tensor = [&](StackTensor &t, size_t n, bool f32) -> cudaError_t {
+    t.n = n; t.f32 = f32;
+    return alloc(&t.ptr, n * (f32 ? 4 : 2));
+  };
+  auto name = [&](const std::string &nm, StackTensor *dst, size_t off, std::vector<int64_t> shape, int layer, int transform = 0) {
+    stack_names[nm] = StackTarget{dst, off, std::move(shape), transform, false, layer};
+  };
+  // ---- weights
+  ENG_CUDA(tensor(M.embed, (size_t)sc->vocab * W, M.f32));
+  ENG_CUDA(tensor(M.head, (size_t)sc->vocab * W, M.f32));
+  name("embed", &M.embed, 0, {sc->vocab, W}, -1);
+  name("head", &M.head, 0, {sc->vocab, W}, -1);
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.final_g), 4));
+  static StackTensor dummy;  // scalars are written through their own small tensors below
+  (void)dummy;
+  size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1;
+  int max_top = 0, max_e = 0;
+  const size_t slots = (size_t)max_batch;
+  std::vector<StackTensor *> scalars;
+  for (int i = 0; i < sc->n_layers; i++) {
+    StackLayer &L = M.layers[(size_t)i];
+    const dis_layer_config &lc = L.c;
+    const std::string pre = "l" + std::to_string(i) + ".";
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&L.g4), 16));
+    if (taps >= 1) {
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&L.canon1), (size_t)W * taps * 4));
+      if (taps > 1) ENG_CUDA(alloc(reinterpret_cast<void **>(&L.cstate1), slots * (taps - 1) * W * 4));
+      if (lc.mlp != DIS_MLP_NONE) {
+        ENG_CUDA(alloc(reinterpret_cast<void **>(&L.canon2), (size_t)W * taps * 4));
+        if (taps > 1) ENG_CUDA(alloc(reinterpret_cast<void **>(&L.cstate2), slots * (taps - 1) * W * 4));
+      }
+    }
+    ENG_CUDA(tensor(L.w_in, (size_t)L.n_in * W, M.f32));
+    max_proj = std::max(max_proj, (size_t)L.n_in);
+    if (lc.mixer == DIS_MIX_LIGHTNING) {
+      const int H = lc.heads, d = lc.dim, dv = lc.vdim;
+      name(pre + "mix.q", &L.w_in, 0, {H * d, W}, i);
+      name(pre + "mix.k", &L.w_in, (size_t)H * d * W, {H * d, W}, i);
+      name(pre + "mix.v", &L.w_in, (size_t)2 * H * d * W, {H * dv, W}, i);
+      name(pre + "mix.g", &L.w_in, (size_t)L.g_off * W, {H * dv, W}, i);
+      ENG_CUDA(tensor(L.w_o, (size_t)W * H * dv, M.f32));
+      name(pre + "mix.o", &L.w_o, 0, {W, H * dv}, i);
+      ENG_CUDA(tensor(L.norm_w, (size_t)H * dv, true));
+      name(pre + "mix.norm", &L.norm_w, 0, {H * dv}, i);
+      ENG_CUDA(tensor(L.decay_d, (size_t)H, true));
+      ENG_CUDA(cudaMemcpy(L.decay_d.ptr, L.decay.data(), (size_t)H * 4, cudaMemcpyHostToDevice));
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&L.state), slots * H * d * dv * 4));
+      max_mix = std::max(max_mix, (size_t)H * dv);
+      max_act = std::max(max_act, (size_t)H * dv);
+    } else if (lc.mixer == DIS_MIX_MINGRU) {
+      const int n = lc.width;
+      name(pre + "mix.z", &L.w_in, 0, {n, W}, i);
+      name(pre + "mix.x", &L.w_in, (size_t)n * W, {n, W}, i);
+      name(pre + "mix.g", &L.w_in, (size_t)2 * n * W, {n, W}, i);
+      ENG_CUDA(tensor(L.b_in, (size_t)3 * n, true));
+      name(pre + "mix.z.b", &L.b_in, 0, {n}, i);
+      name(pre + "mix.x.b", &L.b_in, (size_t)n, {n}, i);
+      ENG_CUDA(tensor(L.w_o, (size_t)W * n, M.f32));
+      name(pre + "mix.o", &L.w_o, 0, {W, n}, i);
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&L.state), slots * n * 4));
+      max_act = std::max(max_act, (size_t)n);
+    } else {
+      const int H = lc.heads, d = lc.dim, dr = lc.rot_dim, dv = lc.vdim, r = lc.kv_rank;
+      name(pre + "mix.q", &L.w_in, 0, {H * (d + dr), W}, i);
+      if (lc.kv_from < 0) {
+        name(pre + "mix.dkv", &L.w_in, (size_t)L.dkv_off * W, {r + dr, W}, i);
+        ENG_CUDA(tensor(L.norm_w, (size_t)r, true));
+        name(pre + "mix.dkv.norm", &L.norm_w, 0, {r}, i);
+      }
+      name(pre + "mix.g", &L.w_in, (size_t)L.g_off * W, {H * dv, W}, i);
+      ENG_CUDA(tensor(L.ukT, (size_t)H * r * d, M.f32));
+      name(pre + "mix.uk", &L.ukT, 0, {H * d, r}, i, /*transpose each head's [d][r] block*/ 1);
+      ENG_CUDA(tensor(L.uv, (size_t)H * dv * r, M.f32));
+      name(pre + "mix.uv", &L.uv, 0, {H * dv, r}, i);
+      ENG_CUDA(tensor(L.sink, (size_t)H, true));
+      name(pre + "mix.sink", &L.sink, 0, {H}, i);
+      ENG_CUDA(tensor(L.w_o, (size_t)W * H * dv, M.f32));
+      name(pre + "mix.o", &L.w_o, 0, {W, H * dv}, i);
+      max_mix = std::max(max_mix, (size_t)H * std::max(r, dv));
+      max_act = std::max(max_act, (size_t)H * dv);
+      max_qf = std::max(max_qf, (size_t)H * (r + dr));
+    }
+    if (lc.mlp == DIS_MLP_DENSE) {
+      const int ff = lc.ff;
+      ENG_CUDA(tensor(L.w_gu, (size_t)2 * ff * W, M.f32));
+      ENG_CUDA(tensor(L.b_gu, (size_t)2 * ff, true));
+      ENG_CUDA(tensor(L.w_down, (size_t)W * ff, M.f32));
+      ENG_CUDA(tensor(L.b_down, (size_t)W, true));
+      name(pre + "mlp.gate", &L.w_gu, 0, {ff, W}, i);
+      name(pre + "mlp.up", &L.w_gu, (size_t)ff * W, {ff, W}, i);
+      name(pre + "mlp.gate.b", &L.b_gu, 0, {ff}, i);
+      name(pre + "mlp.up.b", &L.b_gu, (size_t)ff, {ff}, i);
+      name(pre + "mlp.down", &L.w_down, 0, {W, ff}, i);
+      name(pre + "mlp.down.b", &L.b_down, 0, {W}, i);
+      max_proj = std::max(max_proj, (size_t)2 * ff);
+      max_act = std::max(max_act, (size_t)ff);
+    } else if (lc.mlp == DIS_MLP_MOE) {
+      const int ff = lc.ff, E = lc.experts;
+      ENG_CUDA(tensor(L.w_gu, (size_t)E * 2 * ff * W, M.f32));
+      ENG_CUDA(tensor(L.w_down, (size_t)E * W * ff, M.f32));
+      ENG_CUDA(tensor(L.router, (size_t)E * W, true));
+      name(pre + "mlp.router", &L.router, 0, {E, W}, i);
+      for (int e = 0; e < E; e++) {
+        const std::string ep = pre + "mlp.e" + std::to_string(e) + ".";
+        name(ep + "gate", &L.w_gu, (size_t)e * 2 * ff * W, {ff, W}, i);
+        name(ep + "up", &L.w_gu, ((size_t)e * 2 * ff + ff) * W, {ff, W}, i);
+        name(ep + "down", &L.w_down, (size_t)e * W * ff, {W, ff}, i);
+      }
+      max_proj = std::max(max_proj, (size_t)lc.top * 2 * ff);
+      max_act = std::max(max_act, (size_t)lc.top * ff);
+      max_top = std::max(max_top, lc.top);
+      max_e = std::max(max_e, E);
+    }
+  }
+  // scalar gains and convolution taps are named too; they land in small fp32 areas through views
+  // (a view is a StackTensor that does not own its memory)
+  for (int i = 0; i < sc->n_layers; i++) {
+    StackLayer &L = M.layers[(size_t)i];
+    const std::string pre = "l" + std::to_string(i) + ".";
+    const char *gn[4] = {"norm1", "norm1b", "norm2", "norm2b"};
+    for (int k = 0; k < 4; k++) {
+      if (k >= 2 && L.c.mlp == DIS_MLP_NONE) continue;
+      StackTensor *v = new StackTensor();
+      v->ptr = L.g4 + k; v->n = 1; v->f32 = true;
+      scalars.push_back(v);
+      name(pre + gn[k], v, 0, {}, i);
+    }
+    if (taps >= 1) {
+      StackTensor *v = new StackTensor();
+      v->ptr = L.canon1; v->n = (size_t)W * taps; v->f32 = true;
+      scalars.push_back(v);
+      name(pre + "canon1", v, 0, {W, taps}, i);
+      if (L.c.mlp != DIS_MLP_NONE) {
+        StackTensor *v2 = new StackTensor();
+        v2->ptr = L.canon2; v2->n = (size_t)W * taps; v2->f32 = true;
+        scalars.push_back(v2);
+        name(pre + "canon2", v2, 0, {W, taps}, i);
+      }
+    }
+  }
+  {
+    StackTensor *v = new StackTensor();
+    v->ptr = M.final_g; v->n = 1; v->f32 = true;
+    scalars.push_back(v);
+    name("final.norm", v, 0, {}, -1);
+  }
+  M.views.assign(scalars.begin(), scalars.end());
+  // ---- activations
+  const size_t cap = (size_t)cap_tokens;
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.x), cap * W * 4));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.y), cap * W * 4));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.hn), cap * W * 4));
+  ENG_CUDA(alloc(&M.hc, cap * W * esz));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.proj), cap * max_proj * 4));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.mix), cap * max_mix * 4));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.mix2), cap * max_mix * 4));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.qf), cap * max_qf * 4));
+  ENG_CUDA(alloc(&M.act, cap * max_act * esz));
+  ENG_CUDA(alloc(&M.xr, (size_t)M.max_rows * W * esz));
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.logits), (size_t)M.max_rows * sc->vocab * 4));
+  logits = nullptr;  // the Llama buffer is not allocated; last_logits reads stack->logits
+  if (max_top > 0) {
+    const size_t rows = cap * max_top;
+    M.max_tiles = (int)((rows + kStackGemmTile - 1) / kStackGemmTile) + max_e;
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.r_idx), rows * 4));
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.r_wt), rows * 4));
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.counts), (size_t)max_e * 4));
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.perm_tok), rows * 4));
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.where), rows * 4));
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.tiles), (size_t)(1 + 3 * M.max_tiles) * 4));
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.rows_out), rows * W * 4));
+  }
+  ENG_CUDA(alloc(reinterpret_cast<void **>(&M.d_out), (size_t)2 * M.max_rows * 4));
+  ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&M.h_out), (size_t)2 * M.max_rows * 4));
+  ENG_CUDA(stack_meta(meta_pre, cap_tokens, M.max_rows));
+  cur_meta = &meta_pre;
+  // ---- pages: one pool per latent layer that owns a cache, rows of kv_rank + rot_dim elements; a page id is valid in all
+  {
+    size_t row_bytes = 0;
+    for (auto &L : M.layers) if (L.c.mixer == DIS_MIX_LATENT && L.c.kv_from < 0) row_bytes += (size_t)(L.c.kv_rank + L.c.rot_dim) * esz;
+    int64_t want = c->kv_pages;
+    const int64_t useful = (int64_t)max_batch * max_pages;
+    if (want <= 0) {
+      size_t free_b = 0, total_b = 0;
+      ENG_CUDA(cudaMemGetInfo(&free_b, &total_b));
+      const float frac = c->kv_mem_fraction > 0.f ? c->kv_mem_fraction : 0.85f;
+      want = row_bytes ? (int64_t)((double)free_b * frac / (double)(row_bytes * page_size)) : useful;
+      want = std::min(want, useful);
+    }
+    if (want < 1) return fail(DIS_ERR_OUT_OF_MEMORY, "no device memory left for the latent pages");
+    n_pages = want;
+    for (auto &L : M.layers)
+      if (L.c.mixer == DIS_MIX_LATENT && L.c.kv_from < 0)
+        ENG_CUDA(alloc(&L.pool, (size_t)n_pages * page_size * (L.c.kv_rank + L.c.rot_dim) * esz));
+    pages_ix.init(page_size, n_pages, false);
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&d_page_table), (size_t)max_batch * max_pages * 4));
+    stack_allocs.pop_back();  // freed with the engine's own buffers
+    ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_page_table), (size_t)max_batch * max_pages * sizeof(int)));
+    memset(h_page_table, 0, (size_t)max_batch * max_pages * sizeof(int));
+    (void)any_latent;
+  }
+  seqs.resize((size_t)max_batch);
+  slot_stamp.assign((size_t)max_batch, 0);
+  if (const char *g = getenv("DIS_SAMPLER")) sampler_buckets = strcmp(g, "bisect") != 0;
+  ENG_CUDA(cudaDeviceSynchronize());
+  return DIS_OK;
+}
+
+// bf16 bit patterns or floats on the host -> the target's element type on the device, at an element offset
+int Engine::load_named(const char *nm, const void *host, int dtype, const int64_t *shape, int ndim) {
+  if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
+  if (!stack) return fail(DIS_ERR_INVALID_ARGUMENT, "load_named: this engine holds a Llama model; use load_tensor");
+  if (!nm || !host || (dtype != DIS_F32 && dtype != DIS_BF16) || ndim < 0 || (ndim > 0 && !shape))
+    return fail(DIS_ERR_INVALID_ARGUMENT, "load_named: bad argument");
+  auto it = stack_names.find(nm);
+  if (it == stack_names.end()) return fail(DIS_ERR_INVALID_ARGUMENT, std::string("load_named: the configuration has no tensor '") + nm + "'");
+  StackTarget &t = it->second;
+  std::vector<int64_t> got(shape, shape + ndim);
+  if (got != t.shape) return fail(DIS_ERR_INVALID_ARGUMENT, std::string("load_named: '") + nm + "' has the wrong shape");
+  size_t n = 1;
+  for (int64_t d : got) n *= (size_t)d;
+  std::vector<float> f(n);
+  if (dtype == DIS_F32) memcpy(f.data(), host, n * 4);
+  else for (size_t i = 0; i < n; i++) f[i] = bf16_bits_to_float(reinterpret_cast<const uint16_t *>(host)[i]);
+  if (t.transform == 1) {  // [H*d][r] -> per head [r][d]
+    const dis_layer_config &lc = stack->layers[(size_t)t.layer].c;
+    const size_t H = (size_t)lc.heads, d = (size_t)lc.dim, r = (size_t)lc.kv_rank;
+    std::vector<float> g(n);
+    for (size_t h = 0; h < H; h++)
+      for (size_t a = 0; a < d; a++)
+        for (size_t b = 0; b < r; b++) g[h * r * d + b * d + a] = f[(h * d + a) * r + b];
+    f.swap(g);
+  }
+  ENG_CUDA(cudaSetDevice(cfg.device));
+  if (t.dst->f32) ENG_CUDA(cudaMemcpy(reinterpret_cast<float *>(t.dst->ptr) + t.off, f.data(), n * 4, cudaMemcpyHostToDevice));
+  else {
+    std::vector<uint16_t> b(n);
+    for (size_t i = 0; i < n; i++) b[i] = float_to_bf16_bits(f[i]);
+    ENG_CUDA(cudaMemcpy(reinterpret_cast<uint16_t *>(t.dst->ptr) + t.off, b.data(), n * 2, cudaMemcpyHostToDevice));
+  }
+  t.loaded = true;
+  return DIS_OK;
+}
+
+int Engine::seq_extend(int slot, const uint32_t *tokens, int n, const int *probe, int n_probe) {
+  if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
+  if (!stack) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_extend: only the layer-list family reads given tokens after the prompt");
+  if (slot < 0 || slot >= max_batch || !seqs[(size_t)slot].used) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_extend: no such sequence");
+  if (n < 0 || (n > 0 && !tokens) || n_probe < 0 || (n_probe > 0 && !probe)) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_extend: bad argument");
+  Sequence &s = seqs[(size_t)slot];
+  if ((long long)s.prompt.size() + n >= m.max_ctx) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_extend: the sequence would not fit the context window");
+  for (int i = 0; i < n; i++)
+    if (tokens[i] >= (uint32_t)m.vocab) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_extend: token id out of vocabulary");
+  const int base = (int)s.prompt.size();
+  for (int i = 0; i < n_probe; i++) {
+    if (probe[i] < 0 || probe[i] >= n || (i > 0 && probe[i] <= probe[i - 1])) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_extend: probes must ascend inside the given tokens");
+  }
+  if (!ensure_pages(s, slot, base + n)) return fail(DIS_ERR_OUT_OF_MEMORY, "seq_extend: out of pages");
+  s.prompt.insert(s.prompt.end(), tokens, tokens + n);
+  for (int i = 0; i < n_probe; i++) s.probes.push_back(base + probe[i]);
+  if (n > 0) {
+    s.prefilled = false;                 // the token sampled at the old end, if any, is dropped: the caller gave the continuation
+    if (s.finish == DIS_FINISH_LENGTH || s.finish == DIS_FINISH_STOP || s.finish == DIS_FINISH_STOP_SEQUENCE) s.finish = DIS_FINISH_NONE;
+  }
+  return DIS_OK;
+}
+
+int Engine::seq_probe(int slot, const int *pos, int n) {
+  if (shut) return fail(DIS_ERR_SHUTDOWN, "engine is shut down");
+  if (!stack) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_probe: only the layer-list family keeps logits of prompt positions");
+  if (slot < 0 || slot >= max_batch || !seqs[(size_t)slot].used || n < 0 || (n > 0 && !pos)) return fail(DIS_ERR_INVALID_ARGUMENT, "seq_probe: bad argument");
+  Sequence &s = seqs[(size_t)slot];
+  for (int i = 0; i < n; i++)
+    if (pos[i] < s.len || pos[i] >= (int)s.prompt.size() || (i > 0 && pos[i] <= pos[i - 1]) || (!s.probes.empty() && pos[i] <= s.probes.back() && i == 0))
+      return fail(DIS_ERR_INVALID_ARGUMENT, "seq_probe: positions must ascend, lie among the tokens not yet read, and follow earlier probes");
+  s.probes.insert(s.probes.end(), pos, pos + n);
+  return DIS_OK;
+}
+
+// One pass.  For this family Sequence::prompt is the whole token history: tokens [0, len) are in the state and the cache,
+// [len, size) are waiting; a sequence with nothing waiting feeds the token it sampled last (which then joins the history).
+int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t *out_tokens, int *out_finish, int *out_produced) {
+  StackModel &M = *stack;
+  if (n <= 0 || n > max_batch || !slots || !out_tokens || !out_finish || !out_produced) return fail(DIS_ERR_INVALID_ARGUMENT, "step: bad argument");
+  const uint64_t stamp = ++call_stamp;
+  for (int i = 0; i < n; i++) {
+    if (slots[i] < 0 || slots[i] >= max_batch || !seqs[(size_t)slots[i]].used) return fail(DIS_ERR_INVALID_ARGUMENT, "step: no such sequence");
+    if (slot_stamp[(size_t)slots[i]] == stamp) return fail(DIS_ERR_INVALID_ARGUMENT, "step: duplicate slot");
+    slot_stamp[(size_t)slots[i]] = stamp;
+  }
+  ENG_CUDA(cudaSetDevice(cfg.device));
+  std::vector<int> idx, rem;
+  for (int i = 0; i < n; i++) {
+    Sequence &s = seqs[(size_t)slots[i]];
+    out_tokens[i] = 0; out_produced[i] = 0; out_finish[i] = s.finish;
+    if (s.finish != DIS_FINISH_NONE) continue;
+    const int waiting = (int)s.prompt.size() - s.len;
+    if (waiting == 0 && (!s.prefilled || s.len + 1 > m.max_ctx || !ensure_pages(s, slots[i], s.len + 1))) {
+      s.finish = DIS_FINISH_FAILED; out_finish[i] = s.finish; continue;
+    }
+    idx.push_back(i);
+    rem.push_back(waiting);
+  }
+  if (idx.empty()) { last_rows = 0; return DIS_OK; }
+  std::vector<int> take(idx.size());
+  plan_mixed_step((int)idx.size(), rem.data(), max_prefill_tokens > 0 ? max_prefill_tokens : cap_tokens, cap_tokens, take.data());
+  StepMeta &mt = meta_pre;
+  int T = 0, R = 0, SP = 0, QB = 0;
+  bool all_greedy = true;
+  // rows first: a pass that would produce more logits rows than the engine holds is refused before anything changes
+  {
+    long long rows = 0;
+    for (size_t k = 0; k < idx.size(); k++) {
+      const Sequence &s = seqs[(size_t)slots[idx[k]]];
+      if (take[k] <= 0) continue;
+      const int p0 = s.len, p1 = s.len + take[k];
+      for (int p : s.probes) rows += (p >= p0 && p < p1) ? 1 : 0;
+      rows += (rem[k] == 0 || p1 == (int)s.prompt.size()) ? 1 : 0;
+    }
+    if (rows > M.max_rows) return fail(DIS_ERR_INVALID_ARGUMENT, "step: more logits rows than max_logit_rows");
+  }
+  ENG_CUDA(cudaEventRecord(ev0, stream));
+  for (size_t k = 0; k < idx.size(); k++) {
+    const int i = idx[k];
+    Sequence &s = seqs[(size_t)slots[i]];
+    const int tk = take[k];
+    if (tk <= 0) continue;
+    if (rem[k] == 0) s.prompt.push_back(s.last_token);
+    const int p0 = s.len;
+    for (int j = 0; j < tk; j++) {
+      mt.h<uint32_t>(mt.o_tokens)[T + j] = s.prompt[(size_t)(p0 + j)];
+      mt.h<int>(mt.o_pos)[T + j] = p0 + j;
+      mt.h<int>(mt.o_ptrow)[T + j] = slots[i];
+      mt.h<int>(mt.o_span)[T + j] = SP;
+    }
+    mt.h<int>(mt.o_qb_tok0)[SP] = T;
+    mt.h<int>(mt.o_qb_len)[SP] = tk;
+    mt.h<int>(mt.o_qb_pos0)[SP] = p0;
+    mt.h<int>(mt.o_qb_ptrow)[SP] = slots[i];
+    SP++;
+    for (int j = 0; j < tk; j += stack_bq) {
+      mt.h<int>(mt.o_ab_tok0)[QB] = T + j;
+      mt.h<int>(mt.o_ab_len)[QB] = std::min(stack_bq, tk - j);
+      QB++;
+    }
+    auto row = [&](int tok, float temp, float topp, uint64_t seed, uint64_t step) {
+      mt.h<int>(mt.o_rowmap)[R] = tok;
+      mt.h<float>(mt.o_temp)[R] = temp;
+      mt.h<float>(mt.o_topp)[R] = topp;
+      mt.h<unsigned long long>(mt.o_seed)[R] = seed;
+      mt.h<unsigned long long>(mt.o_step)[R] = step;
+      R++;
+    };
+    for (int p : s.probes)
+      if (p >= p0 && p < p0 + tk) row(T + (p - p0), 0.f, 1.f, 0, 0);
+    if (p0 + tk == (int)s.prompt.size()) {
+      row(T + tk - 1, s.temperature, s.top_p, s.seed, (uint64_t)s.generated);
+      all_greedy = all_greedy && s.temperature <= 0.f;
+    }
+    T += tk;
+  }
+  if (T == 0) { last_rows = 0; return DIS_OK; }
+  if (pt_dirty) {
+    ENG_CUDA(cudaMemcpyAsync(d_page_table, h_page_table, (size_t)max_batch * max_pages * sizeof(int), cudaMemcpyHostToDevice, stream));
+    pt_dirty = false;
+  }
+  ENG_CUDA(cudaMemcpyAsync(mt.dev, mt.host, mt.bytes, cudaMemcpyHostToDevice, stream));
+  ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));
+  if (R > 0) ENG_CUDA(cudaMemcpyAsync(M.h_out, M.d_out, (size_t)2 * M.max_rows * 4, cudaMemcpyDeviceToHost, stream));
+  ENG_CUDA(cudaEventRecord(ev1, stream));
+  ENG_CUDA(cudaEventSynchronize(ev1));
+  float ms = 0.f;
+  ENG_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
+  last_step_ms = ms;
+  last_rows = R;
+  last_T = T;
+  int r = 0;
+  for (size_t k = 0; k < idx.size(); k++) {
+    const int i = idx[k];
+    Sequence &s = seqs[(size_t)slots[i]];
+    const int tk = take[k];
+    if (tk <= 0) continue;
+    const int p0 = s.len;
+    s.len += tk;
+    s.prefill_pos = s.len;
+    size_t keep = 0;
+    for (int p : s.probes) {
+      if (p >= p0 && p < s.len) r++;
+      else s.probes[keep++] = p;
+    }
+    s.probes.resize(keep);
+    if (s.len < (int)s.prompt.size()) continue;  // more chunks to come
+    s.prefilled = true;
+    out_tokens[i] = M.h_out[r];
+    s.last_logprob = reinterpret_cast<const float *>(M.h_out + M.max_rows)[r];
+    finish_check(s, M.h_out[r]);
+    out_finish[i] = s.finish;
+    out_produced[i] = 1;
+    r++;
+  }
+  return DIS_OK;
+}
+
+cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_greedy) {
+  StackModel &M = *stack;
+  StepMeta &mt = meta_pre;
+  const int W = M.c.width, taps = M.c.canon_taps;
+  const float eps = M.c.norm_eps;
+  const bool f32 = M.f32;
+  StackSpans sp{mt.d<uint32_t>(mt.o_tokens), mt.d<int>(mt.o_pos), mt.d<int>(mt.o_ptrow), mt.d<int>(mt.o_span),
+                mt.d<int>(mt.o_qb_tok0), mt.d<int>(mt.o_qb_len), mt.d<int>(mt.o_qb_pos0), mt.d<int>(mt.o_qb_ptrow), T, n_spans};
+  uint64_t &kl = kernel_launches;
+  auto gemm = [&](const void *A, bool a_f32, long long lda, const StackTensor &Wt, size_t w_off, const float *bias, float *out,
+                  int Mrows, int N, int K) -> cudaError_t {
+    StackGemm g;
+    g.A = A; g.a_f32 = a_f32; g.lda = lda;
+    g.W = Wt.f32 ? (const void *)(reinterpret_cast<const float *>(Wt.ptr) + w_off) : (const void *)(reinterpret_cast<const uint16_t *>(Wt.ptr) + w_off);
+    g.w_f32 = Wt.f32; g.ldw = K;
+    g.out = out; g.ldo = N; g.bias = bias; g.M = Mrows; g.N = N; g.K = K;
+    kl++;
+    return launch_stack_gemm(g, stream);
+  };
+  RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, T, W, stream)); kl++;
+  const float *pend_y = nullptr, *pend_post = nullptr;
+  auto sublayer_in = [&](const float *pre, const float *cw, float *cstate) -> cudaError_t {
+    RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, pre, M.hn, T, W, eps, stream)); kl++;
+    pend_y = nullptr;
+    if (taps >= 1) { kl += taps > 1 ? 2 : 1; return launch_stack_canon(M.hn, cw, cstate, sp, M.hc, f32, W, taps, stream); }
+    kl++;
+    return launch_stack_copy_act(M.hn, M.hc, f32, (long long)T * W, stream);
+  };
+  for (size_t li = 0; li < M.layers.size(); li++) {
+    StackLayer &L = M.layers[li];
+    const dis_layer_config &lc = L.c;
+    RET_CUDA(sublayer_in(L.g4 + 0, L.canon1, L.cstate1));
+    const int N = L.n_in;
+    RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W));
+    int n_mix = 0;
+    if (lc.mixer == DIS_MIX_LIGHTNING) {
+      const int H = lc.heads, d = lc.dim, dv = lc.vdim;
+      RET_CUDA(launch_stack_lightning(M.proj, N, reinterpret_cast<const float *>(L.decay_d.ptr), L.state, sp, M.mix, H, d, dv, stream));
+      RET_CUDA(launch_stack_norm_gate(M.mix, reinterpret_cast<const float *>(L.norm_w.ptr), M.proj + L.g_off, N, M.act, f32, T, H * dv, eps, stream));
+      kl += 2;
+      n_mix = H * dv;
+    } else if (lc.mixer == DIS_MIX_MINGRU) {
+      RET_CUDA(launch_stack_mingru(M.proj, N, L.state, sp, M.act, f32, lc.width, stream)); kl++;
+      n_mix = lc.width;
+    } else {
+      const int H = lc.heads, d = lc.dim, dr = lc.rot_dim, dv = lc.vdim, r = lc.kv_rank, D = r + dr;
+      StackLatent sl{H, d, dr, dv, r, lc.rot_dims, lc.rot_base, lc.scale, eps};
+      StackLayer &KV = M.layers[(size_t)L.kv_layer];
+      RET_CUDA(launch_stack_latent_prep(M.proj, N, L.q_off, L.dkv_off, lc.kv_from < 0 ? reinterpret_cast<const float *>(L.norm_w.ptr) : nullptr, sl, sp,
+                                        M.qf, lc.kv_from < 0 ? L.pool : nullptr, f32, d_page_table, max_pages, page_size, stream));
+      // absorbed queries: qf[t][h][0..r) = sum_a q[t][h][a] * uk[h*d + a][.]  (one batch entry per head)
+      StackGemm g;
+      g.A = M.proj + L.q_off; g.a_f32 = true; g.lda = N; g.a_bs = d + dr;
+      g.W = L.ukT.ptr; g.w_f32 = L.ukT.f32; g.ldw = d; g.w_bs = (long long)r * d;
+      g.out = M.qf; g.ldo = (long long)H * D; g.o_bs = D;
+      g.M = T; g.N = r; g.K = d; g.batch = H;
+      RET_CUDA(launch_stack_gemm(g, stream));
+      RET_CUDA(launch_stack_latent_attn(M.qf, KV.pool, f32, reinterpret_cast<const float *>(L.sink.ptr), sl, sp, mt.d<int>(mt.o_ab_tok0),
+                                        mt.d<int>(mt.o_ab_len), n_qb, d_page_table, max_pages, page_size, M.mix, stream));
+      // values: mix2[t][h][0..dv) = sum_b ol[t][h][b] * uv[h*dv + .][b]
+      StackGemm v;
+      v.A = M.mix; v.a_f32 = true; v.lda = (long long)H * r; v.a_bs = r;
+      v.W = L.uv.ptr; v.w_f32 = L.uv.f32; v.ldw = r; v.w_bs = (long long)dv * r;
+      v.out = M.mix2; v.ldo = (long long)H * dv; v.o_bs = dv;
+      v.M = T; v.N = dv; v.K = r; v.batch = H;
+      RET_CUDA(launch_stack_gemm(v, stream));
+      RET_CUDA(launch_stack_gate(M.mix2, M.proj + L.g_off, N, M.act, f32, T, H * dv, stream));
+      kl += 5;
+      n_mix = H * dv;
+    }
+    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, nullptr, M.y, T, W, n_mix));
+    pend_y = M.y; pend_post = L.g4 + 1;
+    if (lc.mlp == DIS_MLP_NONE) continue;
+    RET_CUDA(sublayer_in(L.g4 + 2, L.canon2, L.cstate2));
+    if (lc.mlp == DIS_MLP_DENSE) {
+      const int ff = lc.ff;
+      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W));
+      RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, T, ff, lc.limit, stream)); kl++;
+      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff));
+    } else {
+      const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
+      RET_CUDA(launch_stack_route(M.hc, f32, reinterpret_cast<const float *>(L.router.ptr), T, W, E, top, M.r_idx, M.r_wt, stream));
+      RET_CUDA(launch_stack_moe_plan(M.r_idx, T, top, E, kStackGemmTile, M.counts, M.perm_tok, M.where, M.tiles, M.max_tiles, stream));
+      const int tiles_cap = std::min(M.max_tiles, (rows + kStackGemmTile - 1) / kStackGemmTile + E);
+      StackGemm g;
+      g.A = M.hc; g.a_f32 = f32; g.lda = W; g.a_gather = M.perm_tok;
+      g.W = L.w_gu.ptr; g.w_f32 = L.w_gu.f32; g.ldw = W; g.w_bs = (long long)2 * ff * W;
+      g.out = M.proj; g.ldo = 2 * ff; g.M = rows; g.N = 2 * ff; g.K = W;
+      g.tiles = M.tiles; g.max_tiles = tiles_cap;
+      RET_CUDA(launch_stack_gemm(g, stream));
+      RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, rows, ff, lc.limit, stream));
+      StackGemm dn;
+      dn.A = M.act; dn.a_f32 = f32; dn.lda = ff;
+      dn.W = L.w_down.ptr; dn.w_f32 = L.w_down.f32; dn.ldw = ff; dn.w_bs = (long long)W * ff;
+      dn.out = M.rows_out; dn.ldo = W; dn.M = rows; dn.N = W; dn.K = ff;
+      dn.tiles = M.tiles; dn.max_tiles = tiles_cap;
+      RET_CUDA(launch_stack_gemm(dn, stream));
+      RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, M.y, T, W, top, stream));
+      kl += 6;
+    }
+    pend_y = M.y; pend_post = L.g4 + 3;
+  }
+  // the last sublayer's output joins the residual; rows that need logits get the final norm and the head
+  RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++;
+  if (R <= 0) return cudaSuccess;
+  RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream)); kl++;
+  RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W));
+  const float *temp = mt.d<float>(mt.o_temp), *topp = mt.d<float>(mt.o_topp);
+  const unsigned long long *seed = mt.d<unsigned long long>(mt.o_seed), *step = mt.d<unsigned long long>(mt.o_step);
+  float *d_logprob = reinterpret_cast<float *>(M.d_out + M.max_rows);
+  kl++;
+  if (!all_greedy && sampler_buckets) {
+    TpSampPeers solo{};
+    solo.rank = 0; solo.tp = 1; solo.cap_rows = M.max_rows;
+    return launch_tp_sample(solo, M.logits, M.c.vocab, R, M.c.vocab, temp, topp, seed, step, nullptr, 0, M.d_out, d_logprob, stream);
+  }
+  return launch_sample(M.logits, M.c.vocab, R, M.c.vocab, temp, topp, seed, step, M.d_out, 0, nullptr, nullptr, d_logprob, stream);
+}
+
+}  // namespace dis

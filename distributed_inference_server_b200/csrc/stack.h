@@ -1,0 +1,147 @@
+// stack.h -- layer-list decoders: a model given as a list of layers, each with one token mixer (linear attention with a
+// fixed decay, a minimal gated recurrence, or latent attention over a compressed KV cache) and an optional
+// feed-forward (dense or mixture of experts).  The engine's sequences, page allocator, step planner, sampler and C ABI
+// are shared with the Llama path; this header holds what differs: the per-layer weights, the per-slot recurrent state,
+// the latent page pools and the launchers of k_stack.cu.
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/dis_engine.h"
+#include "common.cuh"
+
+namespace dis {
+
+// ---- k_stack.cu launchers.  `f32` selects the element type of activations and matrices: true = float, false = bf16
+// bit patterns.  Norms, routers, scores, recurrent state and the residual are fp32 in both.
+struct StackGemm {
+  const void *A = nullptr;      // [M][K] activations: float when a_f32, else bf16
+  const void *W = nullptr;      // [N][K] weights: float when w_f32, else bf16; applied as A W^T
+  float *out = nullptr;         // [M][N] fp32
+  const float *bias = nullptr;  // [N] or null
+  int M = 0, N = 0, K = 0;
+  long long lda = 0, ldw = 0, ldo = 0;
+  bool a_f32 = true, w_f32 = true;
+  // batch (blockIdx.z): element offsets added per batch index
+  int batch = 1;
+  long long a_bs = 0, w_bs = 0, o_bs = 0, bias_bs = 0;
+  // grouped rows (mixture of experts): tiles[0] = number of row tiles, then {group, row0, rows} per tile; the group
+  // selects the weight block (w_bs) -- M is then the capacity of the row space and max_tiles the grid's extent
+  const int *tiles = nullptr;
+  int max_tiles = 0;
+  const int *a_gather = nullptr;  // row r of the row space reads A row a_gather[r]
+};
+cudaError_t launch_stack_gemm(const StackGemm &g, cudaStream_t st);
+
+struct StackSpans {  // device arrays of the pass
+  const uint32_t *tokens;  // [T]
+  const int *pos;          // [T] position of the token in its sequence
+  const int *slot;         // [T] sequence slot
+  const int *span;         // [T] index of the token's span
+  const int *sp_tok0, *sp_len, *sp_pos0, *sp_slot;  // [n_spans]
+  int T, n_spans;
+};
+
+cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, int T, int W, cudaStream_t st);
+// x += unit_rms(y) * post (when y), then hn = unit_rms(x) * pre (when hn).  post / pre: device scalars.
+cudaError_t launch_stack_resid_norm(float *x, const float *y, const float *post, const float *pre, float *hn, int T, int W,
+                                    float eps, cudaStream_t st);
+// hc = hn + causal depthwise convolution over time (taps >= 1), reading the taps-1 inputs before a span from `state`
+// ([slots][taps-1][W]); then the state is replaced by the span's last taps-1 inputs (second launch inside).
+cudaError_t launch_stack_canon(const float *hn, const float *w, float *state, const StackSpans &sp, void *hc, bool f32, int W,
+                               int taps, cudaStream_t st);
+cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st);
+// proj [T][ld]: q at 0, k at H*d, v at 2*H*d (pre-activation).  state [slots][H][d][dv].  o [T][H*dv] fp32.
+cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
+                                   float *o, int H, int d, int dv, cudaStream_t st);
+// out = unit_rms(o) * w * sigmoid(gate) per token over n = H*dv coordinates; gate [T][ldg]
+cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *gate, long long ldg, void *out, bool f32, int T,
+                                   int n, float eps, cudaStream_t st);
+// out = o * sigmoid(gate)
+cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, void *out, bool f32, int T, int n, cudaStream_t st);
+// proj [T][ld]: z at 0, u at n, g at 2n (biases already added).  state [slots][n].
+cudaError_t launch_stack_mingru(const float *proj, long long ld, float *state, const StackSpans &sp, void *out, bool f32, int n,
+                                cudaStream_t st);
+// Latent attention, step 1: per token, the rotated query parts go to qf[T][H][r+dr] (+r), and -- when pool is given --
+// the normed latent and the rotated shared key part go to the token's row of the page pool ([pages*page_size][r+dr]).
+struct StackLatent {
+  int H, d, dr, dv, r, rot_dims;
+  float rot_base, scale, eps;
+};
+cudaError_t launch_stack_latent_prep(const float *proj, long long ld, int q_off, int dkv_off, const float *dkv_norm,
+                                     const StackLatent &c, const StackSpans &sp, float *qf, void *pool, bool f32,
+                                     const int *page_table, int max_pages, int page_size, cudaStream_t st);
+// step 2: scores of qf against the pool rows of the sequence (causal, softmax with a per-head sink in the denominator),
+// output the weighted sum of the latents: ol [T][H][r] fp32.  qb_tok0 / qb_len: query blocks (tokens of one span).
+int stack_latent_block_tokens(const StackLatent &c);
+cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32, const float *sink, const StackLatent &c,
+                                     const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb,
+                                     const int *page_table, int max_pages, int page_size, float *ol, cudaStream_t st);
+// act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu [M][2*ff] (gate | up)
+cudaError_t launch_stack_glu(const float *gu, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit, cudaStream_t st);
+// Router: logits in fp32 from hc and the fp32 router matrix; top-k by value (lowest index wins a tie); softmax over the chosen.
+cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
+                               cudaStream_t st);
+// Row plan of the experts: counts / cursor [E] ints (zeroed inside), perm_tok [T*top], where [T*top] (row of (t, k)),
+// tiles [1 + 3 * max_tiles], rows_total[1]
+cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
+                                  int *tiles, int max_tiles, cudaStream_t st);
+cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, float *y, int T, int W, int top,
+                                     cudaStream_t st);
+cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const float *g, void *out, bool f32, int R, int W, float eps,
+                                    cudaStream_t st);
+constexpr int kStackGemmTile = 64;
+
+// ---- the model
+struct StackTensor {
+  void *ptr = nullptr;
+  size_t n = 0;
+  bool f32 = true;
+  std::vector<int64_t> shape;
+  bool loaded = false;
+};
+
+struct StackLayer {
+  dis_layer_config c{};
+  std::vector<float> decay;
+  // mixer
+  StackTensor w_in;     // fused input projection rows (see stack.cu for the row order per mixer)
+  StackTensor b_in;     // its bias (fp32) or empty
+  StackTensor w_o;      // output projection
+  StackTensor norm_w;   // lightning: gain of the head norm; latent: gain of the latent norm (fp32)
+  StackTensor ukT;      // latent: per head [r][d] = transpose of the head's block of the key up-projection
+  StackTensor uv;       // latent: [H*dv][r]
+  StackTensor sink;     // latent: [H] fp32
+  StackTensor decay_d;  // lightning: [H] fp32
+  int n_in = 0, q_off = 0, dkv_off = 0, g_off = 0;
+  int kv_layer = -1;    // latent: index of the layer whose pool this layer reads (itself when it owns one)
+  void *pool = nullptr; // latent with a pool of its own
+  float *state = nullptr;   // lightning [slots][H][d][dv]; mingru [slots][n]
+  float *canon1 = nullptr, *canon2 = nullptr;        // [W][taps] fp32
+  float *cstate1 = nullptr, *cstate2 = nullptr;      // [slots][taps-1][W]
+  float *g4 = nullptr;  // device: norm1, norm1b, norm2, norm2b
+  // feed-forward
+  StackTensor w_gu, b_gu, w_down, b_down;  // dense: [2ff][W], [2ff], [W][ff], [W]; experts: stacked per expert
+  StackTensor router;                      // [E][W] fp32
+};
+
+struct StackModel {
+  dis_stack_config c{};
+  bool f32 = false;
+  std::vector<StackLayer> layers;
+  StackTensor embed, head;
+  float *final_g = nullptr;
+  std::vector<StackTensor *> views;  // named scalars and taps: tensors that point into areas owned elsewhere
+  int max_rows = 0;
+  // activations
+  float *x = nullptr, *y = nullptr, *hn = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *qf = nullptr, *logits = nullptr;
+  void *hc = nullptr, *act = nullptr, *xr = nullptr;
+  // experts
+  int *r_idx = nullptr, *counts = nullptr, *perm_tok = nullptr, *where = nullptr, *tiles = nullptr;
+  float *r_wt = nullptr, *rows_out = nullptr;
+  int max_tiles = 0;
+  uint32_t *d_out = nullptr, *h_out = nullptr;  // [max_rows] ids then [max_rows] log-probabilities
+};
+
+}  // namespace dis

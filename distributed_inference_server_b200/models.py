@@ -1,0 +1,301 @@
+"""Model registry: which engine a model folder's config.json asks for, and how its weights get there.
+
+A model folder holds config.json and model.safetensors.  `architecture` (or, for Hugging Face style folders,
+`architectures[0]` / `model_type`) selects an entry of ARCHITECTURES; the entry turns the configuration into the
+engine's description of the model and names every tensor.  Two families exist:
+
+  llama     the fixed Llama decoder of engine.cu (ModelShape; tensors by kind and layer)
+  Kidolorn  a layer-list decoder of stack.cu (StackSpec; tensors by name): per layer one mixer out of linear attention
+            with a fixed per-head decay, a minimal gated recurrence, or latent attention over a compressed cache (which a
+            later layer may share), and a dense or mixture-of-experts feed-forward, every sublayer behind a scalar-gain RMS
+            norm and a short causal convolution.
+
+The reference has no model loading at all (crates/inference/src/worker.rs:1 is empty).
+"""
+from __future__ import annotations
+
+import json
+import mmap
+import os
+import struct
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterator, List, Optional, Tuple
+
+import numpy as np
+
+from . import binding as B
+
+_MIXERS = {"lightning": B.MIX_LIGHTNING, "mingru": B.MIX_MINGRU, "latent_attention": B.MIX_LATENT}
+
+
+@dataclass
+class LayerSpec:
+    mixer: str
+    heads: int = 0
+    dim: int = 0
+    vdim: int = 0
+    width: int = 0
+    kv_rank: int = 0
+    rot_dim: int = 0
+    rot_dims: int = 0
+    kv_from: int = -1
+    rot_base: float = 10000.0
+    scale: float = 1.0
+    decay: List[float] = field(default_factory=list)
+    mlp: str = "none"  # none | dense | moe
+    ff: int = 0
+    experts: int = 0
+    top: int = 0
+    limit: float = 0.0
+
+
+@dataclass
+class StackSpec:
+    """A layer-list decoder: sizes, constants and the order of layers, all from the model's configuration."""
+    name: str
+    vocab: int
+    width: int
+    layers: List[LayerSpec]
+    canon_taps: int = 0
+    norm_eps: float = 1e-5
+
+    def tensor_shapes(self) -> Dict[str, Tuple[int, ...]]:
+        """Every tensor of the model file, by name."""
+        W, out = self.width, {"embed": (self.vocab, self.width), "head": (self.vocab, self.width), "final.norm": ()}
+        for i, L in enumerate(self.layers):
+            p = f"l{i}."
+            out[p + "norm1"] = out[p + "norm1b"] = ()
+            if self.canon_taps >= 1:
+                out[p + "canon1"] = (W, self.canon_taps)
+            if L.mixer == "lightning":
+                out.update({p + "mix.q": (L.heads * L.dim, W), p + "mix.k": (L.heads * L.dim, W), p + "mix.v": (L.heads * L.vdim, W),
+                            p + "mix.g": (L.heads * L.vdim, W), p + "mix.o": (W, L.heads * L.vdim), p + "mix.norm": (L.heads * L.vdim,)})
+            elif L.mixer == "mingru":
+                out.update({p + "mix.z": (L.width, W), p + "mix.z.b": (L.width,), p + "mix.x": (L.width, W), p + "mix.x.b": (L.width,),
+                            p + "mix.g": (L.width, W), p + "mix.o": (W, L.width)})
+            else:
+                out[p + "mix.q"] = (L.heads * (L.dim + L.rot_dim), W)
+                if L.kv_from < 0:
+                    out[p + "mix.dkv"] = (L.kv_rank + L.rot_dim, W)
+                    out[p + "mix.dkv.norm"] = (L.kv_rank,)
+                out.update({p + "mix.uk": (L.heads * L.dim, L.kv_rank), p + "mix.uv": (L.heads * L.vdim, L.kv_rank),
+                            p + "mix.sink": (L.heads,), p + "mix.g": (L.heads * L.vdim, W), p + "mix.o": (W, L.heads * L.vdim)})
+            if L.mlp == "none":
+                continue
+            out[p + "norm2"] = out[p + "norm2b"] = ()
+            if self.canon_taps >= 1:
+                out[p + "canon2"] = (W, self.canon_taps)
+            if L.mlp == "dense":
+                out.update({p + "mlp.gate": (L.ff, W), p + "mlp.gate.b": (L.ff,), p + "mlp.up": (L.ff, W), p + "mlp.up.b": (L.ff,),
+                            p + "mlp.down": (W, L.ff), p + "mlp.down.b": (W,)})
+            else:
+                out[p + "mlp.router"] = (L.experts, W)
+                for e in range(L.experts):
+                    out.update({f"{p}mlp.e{e}.gate": (L.ff, W), f"{p}mlp.e{e}.up": (L.ff, W), f"{p}mlp.e{e}.down": (W, L.ff)})
+        return out
+
+    def c(self, max_ctx: int, max_logit_rows: int, f32: bool):
+        """The C description (dis_stack_config) and the objects that must outlive the call that reads it."""
+        arr = (B.LayerConfig * len(self.layers))()
+        keep = [arr]
+        for i, L in enumerate(self.layers):
+            c = arr[i]
+            c.mixer = _MIXERS[L.mixer]
+            c.heads, c.dim, c.vdim, c.width = L.heads, L.dim, L.vdim, L.width
+            c.kv_rank, c.rot_dim, c.rot_dims, c.kv_from = L.kv_rank, L.rot_dim, L.rot_dims, L.kv_from
+            c.rot_base, c.scale = L.rot_base, L.scale
+            if L.decay:
+                d = (B.C.c_float * len(L.decay))(*L.decay)
+                keep.append(d)
+                c.decay = d
+            c.mlp = {"none": B.MLP_NONE, "dense": B.MLP_DENSE, "moe": B.MLP_MOE}[L.mlp]
+            c.ff, c.experts, c.top, c.limit = L.ff, L.experts, L.top, L.limit
+        sc = B.StackConfig(self.vocab, self.width, len(self.layers), self.canon_taps, max_ctx, max_logit_rows,
+                           B.F32 if f32 else B.BF16, self.norm_eps, arr)
+        return sc, keep
+
+
+def kidolorn_spec(cfg: dict) -> StackSpec:
+    """Kidolorn's config.json -> StackSpec.  Every size and constant comes from the file; nothing is assumed."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        kind, mx = ly["type"], ly["mixer"]
+        if kind not in _MIXERS:
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        L = LayerSpec(kind)
+        if kind == "lightning":
+            L.heads, L.dim, L.vdim = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"])
+            L.decay = [float(a) for a in mx["decay"]]
+            if len(L.decay) != L.heads:
+                raise ValueError(f"layer {i}: decay must list one value per head")
+        elif kind == "mingru":
+            L.width = int(mx["width"])
+        else:
+            L.heads, L.dim, L.vdim = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"])
+            L.kv_rank, L.rot_dim = int(mx["kv_rank"]), int(mx["rot_dim"])
+            rot = mx.get("rot") or {}
+            L.rot_dims, L.rot_base = int(rot.get("dims", L.rot_dim)), float(rot.get("base", 10000.0))
+            L.scale = float(mx["scale"])
+            kf = mx.get("kv_from")
+            L.kv_from = -1 if kf is None else int(kf)
+        ml = ly.get("mlp")
+        if ml is not None:
+            if ml["kind"] == "dense":
+                L.mlp, L.ff, L.limit = "dense", int(ml["ff"]), float(ml["limit"])
+            elif ml["kind"] == "moe":
+                L.mlp, L.ff, L.limit = "moe", int(ml["expert"]["ff"]), float(ml["expert"]["limit"])
+                L.experts, L.top = int(ml["router"]["experts"]), int(ml["router"]["top"])
+            else:
+                raise ValueError(f"layer {i}: unknown feed-forward kind {ml['kind']!r}")
+        layers.append(L)
+    canon = cfg.get("canon") or {}
+    return StackSpec("Kidolorn", int(cfg["vocab"]), int(cfg["width"]), layers, int(canon.get("taps", 0)),
+                     float((cfg.get("norm") or {}).get("eps", 1e-5)))
+
+
+def llama_shape(cfg: dict):
+    """A Hugging Face style Llama config.json -> ModelShape."""
+    from .worker import ModelShape
+    nh = int(cfg["num_attention_heads"])
+    return ModelShape(int(cfg["vocab_size"]), int(cfg["hidden_size"]), int(cfg["num_hidden_layers"]), nh,
+                      int(cfg.get("num_key_value_heads", nh)), int(cfg.get("head_dim", int(cfg["hidden_size"]) // nh)),
+                      int(cfg["intermediate_size"]), int(cfg.get("max_position_embeddings", 8192)),
+                      float(cfg.get("rope_theta", 10000.0)), float(cfg.get("rms_norm_eps", 1e-5)))
+
+
+# architecture name -> (family, configuration reader)
+ARCHITECTURES: Dict[str, Tuple[str, Callable[[dict], object]]] = {
+    "Kidolorn": ("stack", kidolorn_spec),
+    "LlamaForCausalLM": ("llama", llama_shape),
+    "llama": ("llama", llama_shape),
+}
+
+
+def architecture_of(cfg: dict) -> str:
+    name = cfg.get("architecture") or (cfg.get("architectures") or [None])[0] or cfg.get("model_type")
+    if name not in ARCHITECTURES:
+        raise ValueError(f"config.json names architecture {name!r}; known: {sorted(ARCHITECTURES)}")
+    return name
+
+
+def read_config(model_dir: str):
+    """(family, description) of the model in `model_dir`."""
+    cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    family, reader = ARCHITECTURES[architecture_of(cfg)]
+    return family, reader(cfg)
+
+
+_ST_DTYPES = {"BF16": (np.uint16, B.BF16), "F32": (np.float32, B.F32), "I32": (np.int32, None)}
+
+
+def read_safetensors(path: str) -> Iterator[Tuple[str, np.ndarray, Optional[int], Tuple[int, ...]]]:
+    """Tensors of a safetensors file: (name, flat array, engine dtype code or None, shape).  The file is an 8-byte
+    little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets), then the data; bfloat16
+    comes back as its uint16 bit patterns."""
+    with open(path, "rb") as f:
+        n = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(n))
+        mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+    base = 8 + n
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        if info["dtype"] not in _ST_DTYPES:
+            raise ValueError(f"{name}: dtype {info['dtype']} is not supported")
+        npdt, code = _ST_DTYPES[info["dtype"]]
+        a, e = info["data_offsets"]
+        arr = np.frombuffer(mm, dtype=npdt, count=(e - a) // np.dtype(npdt).itemsize, offset=base + a)
+        yield name, arr, code, tuple(int(d) for d in info["shape"])
+
+
+_LLAMA_NAMES = {"input_layernorm.weight": B.T_ATTN_NORM, "self_attn.q_proj.weight": B.T_WQ, "self_attn.k_proj.weight": B.T_WK,
+                "self_attn.v_proj.weight": B.T_WV, "self_attn.o_proj.weight": B.T_WO, "post_attention_layernorm.weight": B.T_MLP_NORM,
+                "mlp.gate_proj.weight": B.T_WGATE, "mlp.up_proj.weight": B.T_WUP, "mlp.down_proj.weight": B.T_WDOWN}
+
+
+def load_model(model_dir: str, dtype: str = "bfloat16", max_batch: int = 32, max_tokens: int = 0, page_size: int = 64,
+               max_step_tokens: int = 0, max_logit_rows: int = 0, max_ctx: int = 0, device: int = 0, flags: int = 0,
+               eos_token: int = -1):
+    """Create an engine for the model in `model_dir`, load its weights and finalize it.
+
+    max_tokens: tokens the cache pool holds (rounded up to pages); 0 = a share of free memory.  dtype float32 is available
+    for layer-list models only."""
+    from .worker import Engine, WorkerConfig
+    family, desc = read_config(model_dir)
+    if dtype not in ("bfloat16", "float32"):
+        raise ValueError("dtype must be bfloat16 or float32")
+    pages = (max_tokens + page_size - 1) // page_size if max_tokens > 0 else 0
+    st = os.path.join(model_dir, "model.safetensors")
+    if family == "stack":
+        ctx = max_ctx or (max_tokens + page_size if max_tokens > 0 else 8192)
+        eng = Engine(WorkerConfig(None, device=device, max_batch=max_batch, max_step_tokens=max_step_tokens, page_size=page_size,
+                                  kv_pages=pages, flags=flags, eos_token=eos_token, stack=desc, context_size=ctx,
+                                  compute_dtype=dtype, max_logit_rows=max_logit_rows))
+        want = desc.tensor_shapes()
+        for name, arr, code, shape in read_safetensors(st):
+            if name not in want:
+                raise ValueError(f"{st}: tensor {name!r} is not part of this configuration")
+            if code is None:
+                raise ValueError(f"{st}: {name!r} is an integer table; this design has none")
+            eng.load_named(name, arr, shape)
+        eng.finalize()
+        return eng
+    if dtype != "bfloat16":
+        raise ValueError("the Llama engine computes in bfloat16 only")
+    import dataclasses
+    shape = dataclasses.replace(desc, max_ctx=max_ctx) if max_ctx else desc
+    eng = Engine(WorkerConfig(shape, device=device, max_batch=max_batch, max_step_tokens=max_step_tokens, page_size=page_size,
+                              kv_pages=pages, flags=flags, eos_token=eos_token))
+    seen_head = False
+    for name, arr, code, _ in read_safetensors(st):
+        if code is None:
+            continue
+        if name == "model.embed_tokens.weight":
+            eng.load_tensor(B.T_EMBED, 0, arr)
+        elif name == "model.norm.weight":
+            eng.load_tensor(B.T_FINAL_NORM, 0, arr)
+        elif name == "lm_head.weight":
+            eng.load_tensor(B.T_LM_HEAD, 0, arr)
+            seen_head = True
+        elif name.startswith("model.layers."):
+            _, _, li, rest = name.split(".", 3)
+            if rest in _LLAMA_NAMES:
+                eng.load_tensor(_LLAMA_NAMES[rest], int(li), arr)
+    if not seen_head:  # tied embeddings
+        for name, arr, code, _ in read_safetensors(st):
+            if name == "model.embed_tokens.weight":
+                eng.load_tensor(B.T_LM_HEAD, 0, arr)
+    eng.finalize()
+    return eng
+
+
+def random_tensors(spec: StackSpec, seed: int = 0, scale: float = 1.0) -> Dict[str, np.ndarray]:
+    """Random float32 weights for a layer-list model (benchmarks and tests): matrices ~ N(0, 1/fan_in), gains and
+    convolution taps small, rounded to bfloat16-representable values so that every compute dtype sees the same model."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in spec.tensor_shapes().items():
+        leaf = name.rsplit(".", 1)[-1]
+        if shape == ():
+            a = np.asarray(rng.uniform(0.5, 1.5), np.float32)
+        elif leaf.startswith("canon"):
+            a = rng.normal(0, 0.3, shape).astype(np.float32)
+        elif leaf in ("norm",) or name.endswith("dkv.norm"):
+            a = rng.uniform(0.5, 1.5, shape).astype(np.float32)
+        elif leaf == "sink":
+            a = rng.normal(0, 1.0, shape).astype(np.float32)
+        elif leaf == "b":
+            a = rng.normal(0, 0.3, shape).astype(np.float32)
+        elif name in ("embed",):
+            a = rng.normal(0, 1.0, shape).astype(np.float32)
+        else:
+            a = (rng.standard_normal(shape, dtype=np.float32) * np.float32(scale / np.sqrt(shape[-1])))
+        out[name] = bf16_round(a)
+    return out
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    """float32 values rounded to the nearest bfloat16 (ties to even), returned as float32."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).reshape(np.shape(a))

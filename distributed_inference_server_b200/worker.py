@@ -144,6 +144,9 @@ class WorkerConfig:  # design.md:316-322 + GPU-engine fields
     synthetic_seed: int = 0
     stream: int = 0
     nccl_id: Optional[bytes] = None
+    stack: Optional[object] = None  # models.StackSpec: a layer-list model instead of `model` (dis_engine_create_stack)
+    compute_dtype: str = "bfloat16"  # layer-list models: "bfloat16" or "float32"
+    max_logit_rows: int = 0  # layer-list models: logits rows one pass may return (sampled rows + probed positions)
 
 
 class Engine:
@@ -152,9 +155,10 @@ class Engine:
     def __init__(self, cfg: WorkerConfig):
         self.lib = B.load()
         c = B.EngineConfig()
-        c.model = cfg.model.c()
-        if cfg.context_size:
-            c.model.max_ctx = cfg.context_size
+        if cfg.stack is None:
+            c.model = cfg.model.c()
+            if cfg.context_size:
+                c.model.max_ctx = cfg.context_size
         c.device, c.tp_rank, c.tp_size = cfg.device, cfg.tp_rank, cfg.tp_size
         c.max_batch, c.max_step_tokens, c.page_size = cfg.max_batch, cfg.max_step_tokens, cfg.page_size
         c.kv_pages, c.kv_mem_fraction, c.flags, c.eos_token = cfg.kv_pages, cfg.kv_mem_fraction, cfg.flags, cfg.eos_token
@@ -162,11 +166,16 @@ class Engine:
         if cfg.nccl_id:
             C.memmove(c.nccl_id, cfg.nccl_id, 128)
         self.h = C.c_void_p()
-        rc = self.lib.dis_engine_create(C.byref(c), C.byref(self.h))
+        if cfg.stack is not None:
+            sc, keep = cfg.stack.c(cfg.context_size or 8192, cfg.max_logit_rows, cfg.compute_dtype == "float32")
+            rc = self.lib.dis_engine_create_stack(C.byref(c), C.byref(sc), C.byref(self.h))
+            del keep
+        else:
+            rc = self.lib.dis_engine_create(C.byref(c), C.byref(self.h))
         if rc != B.OK:
             self.h = None
             raise WorkerError(_KIND[rc], self.lib.dis_last_error().decode())
-        self.vocab = cfg.model.vocab
+        self.vocab = cfg.stack.vocab if cfg.stack is not None else cfg.model.vocab
 
     def _check(self, rc: int):
         if rc != B.OK:
@@ -195,6 +204,37 @@ class Engine:
         else:
             raise TypeError("load_tensor: float32 values or uint16 bf16 bit patterns")
         self._check(self.lib.dis_engine_load_tensor(self.h, kind, layer, arr.ctypes.data, dt))
+
+    def load_named(self, name: str, arr: np.ndarray, shape=None):
+        """A tensor of a layer-list model by its name in the model file: float32 values or uint16 bf16 bit patterns."""
+        shape = tuple(arr.shape if shape is None else shape)
+        arr = np.ascontiguousarray(arr)
+        if arr.dtype == np.float32:
+            dt = B.F32
+        elif arr.dtype == np.uint16:
+            dt = B.BF16
+        else:
+            raise TypeError("load_named: float32 values or uint16 bf16 bit patterns")
+        sh = (C.c_int64 * max(1, len(shape)))(*shape)
+        self._check(self.lib.dis_engine_load_named(self.h, name.encode(), arr.ctypes.data, dt, sh, len(shape)))
+
+    def seq_extend(self, slot: int, tokens: Sequence[int], probe: Sequence[int] = ()):
+        """Teacher forcing: append given tokens to a live sequence; `probe` lists offsets into them whose logits are kept."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        pr = np.ascontiguousarray(probe, dtype=np.int32)
+        self._check(self.lib.dis_engine_seq_extend(self.h, slot, t.ctypes.data if len(t) else None, len(t),
+                                                   pr.ctypes.data if len(pr) else None, len(pr)))
+
+    def seq_probe(self, slot: int, positions: Sequence[int]):
+        """Keep the logits at these absolute positions (ascending, not yet read) of a live sequence."""
+        pr = np.ascontiguousarray(positions, dtype=np.int32)
+        if len(pr):
+            self._check(self.lib.dis_engine_seq_probe(self.h, slot, pr.ctypes.data, len(pr)))
+
+    def last_logit_rows(self) -> int:
+        n = C.c_int32(0)
+        self._check(self.lib.dis_engine_last_logit_rows(self.h, C.byref(n)))
+        return n.value
 
     def read_tensor(self, kind: int, layer: int) -> np.ndarray:
         n = C.c_size_t(0)

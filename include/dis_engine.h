@@ -410,6 +410,67 @@ DIS_API int dis_k_sample_vocab_parallel(const float *logits, int32_t T, int32_t 
 DIS_API int dis_k_synth_bf16(uint16_t *dst, size_t n, uint64_t seed, int32_t kind, int32_t layer, float amp,
                              float offset, void *stream);
 
+/* ---- layer-list decoders ------------------------------------------------------------------------ *
+ * A second model family beside the Llama decoder: the model is a list of layers, each one token mixer plus an
+ * optional feed-forward.  Every layer is  x += post1(mixer(conv(pre1(x))));  x += post2(ff(conv(pre2(x))))  with
+ * scalar-gain RMS norms and a short causal depthwise convolution (canon_taps taps, 0 = none) in front of each
+ * sublayer.  The engine's sequences, pages, step planner, sampler and serving loop are the same as for Llama;
+ * sequences additionally own a slot of recurrent state (linear-attention matrices, gated-recurrence vectors and
+ * the convolutions' last inputs).  The reference has no counterpart (its model family is Llama only). */
+typedef enum dis_mixer_kind {
+  DIS_MIX_LIGHTNING = 0, /* linear attention, fixed decay per head: S = a S + k v^T, o = S^T q; q, k, v through SiLU; head-wise
+                            outputs RMS-normed together, gated by a sigmoid */
+  DIS_MIX_MINGRU = 1,    /* S = (1 - z) S + z c with z, c from the current token only; output S * silu(gate) */
+  DIS_MIX_LATENT = 2     /* softmax attention over a cached low-rank latent + one rotated key part shared by the heads,
+                            with a per-head sink term in the denominator and a sigmoid output gate */
+} dis_mixer_kind;
+typedef enum dis_mlp_kind { DIS_MLP_NONE = 0, DIS_MLP_DENSE = 1, DIS_MLP_MOE = 2 } dis_mlp_kind;
+
+typedef struct dis_layer_config {
+  int32_t mixer;                 /* dis_mixer_kind */
+  int32_t heads, dim, vdim;      /* lightning, latent: heads, query/key size (latent: its unrotated part), value size */
+  int32_t width;                 /* mingru: size of the recurrence */
+  int32_t kv_rank, rot_dim;      /* latent: size of the cached latent, size of the rotated query/key part */
+  int32_t rot_dims;              /* latent: leading coordinates of the rotated part that are rotated (pairs i, i + rot_dims/2) */
+  int32_t kv_from;               /* latent: layer whose cache this layer reads; -1 = its own */
+  float rot_base, scale;         /* latent: rotary base; factor on the scores */
+  const float *decay;            /* lightning: [heads] */
+  int32_t mlp;                   /* dis_mlp_kind */
+  int32_t ff;                    /* hidden size of the feed-forward (of one expert) */
+  int32_t experts, top;          /* mixture of experts: how many, how many per token */
+  float limit;                   /* clamp of the gate (above) and up (both sides) branches */
+} dis_layer_config;
+
+typedef struct dis_stack_config {
+  int32_t vocab, width, n_layers;
+  int32_t canon_taps;            /* taps of the input convolutions; 0 = none */
+  int32_t max_ctx;               /* longest sequence */
+  int32_t max_logit_rows;        /* logits rows one pass can return (sampled rows + probed prompt positions); 0 = max_batch */
+  int32_t compute_dtype;         /* DIS_BF16: matrices and their inputs in bf16, fp32 accumulation; DIS_F32: everything fp32 */
+  float norm_eps;
+  const dis_layer_config *layers;
+} dis_stack_config;
+
+/* cfg->model is ignored (model_info reports vocab, width, layers and max_ctx of the stack); tensor parallelism and the
+ * prefix cache are not available for this family and are refused. */
+DIS_API int dis_engine_create_stack(const dis_engine_config *cfg, const dis_stack_config *stack, dis_engine **out);
+/* Tensors by the names of the model's file: "embed", "head", "final.norm", "l<i>.norm1", "l<i>.mix.q", "l<i>.mlp.e<j>.up", ...
+ * `shape` is checked against the configuration.  dtype: DIS_F32 values or DIS_BF16 bit patterns. */
+DIS_API int dis_engine_load_named(dis_engine *e, const char *name, const void *host, int dtype, const int64_t *shape,
+                                  int32_t ndim);
+/* Teacher forcing: append `n` given tokens to a live sequence.  The next passes read them as prompt tokens (in chunks,
+ * beside other sequences' decode rows, like any prompt); a token sampled earlier and not yet fed is dropped.  `probe`
+ * lists offsets into `tokens` whose logits the pass that reads them keeps: the rows of dis_engine_last_logits are then,
+ * for each listed sequence in order, its probed positions in ascending order followed by its sampled row (if the pass
+ * reached the end of its tokens).  Works for both model families; probing needs max_logit_rows (stack) to hold them. */
+DIS_API int dis_engine_seq_extend(dis_engine *e, int32_t slot, const uint32_t *tokens, int32_t n, const int32_t *probe,
+                                  int32_t n_probe);
+/* Mark positions of a live sequence (absolute, ascending, among its tokens that no pass has read yet) whose logits the
+ * pass that reads them keeps, as `probe` of dis_engine_seq_extend does for the tokens it appends. */
+DIS_API int dis_engine_seq_probe(dis_engine *e, int32_t slot, const int32_t *positions, int32_t n);
+/* Logits rows the last pass produced. */
+DIS_API int dis_engine_last_logit_rows(dis_engine *e, int32_t *n_rows);
+
 #ifdef __cplusplus
 }
 #endif
