@@ -181,10 +181,10 @@ cudaError_t launch_stack_latent_prep(const float *proj, long long ld, int q_off,
 constexpr int kLatTile = 32, kLatWarps = 8, kLatMaxR = 1024;
 
 int stack_latent_block_tokens(const StackLatent &c) {
-  // shared memory: tile [32][D+1] + per pair (D query + r accumulators + 2)
+  // shared memory: tile [32][D+1] + [warps][32] weights + per pair (D query + r accumulators + 2)
   const int D = c.r + c.dr;
   int bq = 8;
-  while (bq > 1 && ((size_t)kLatTile * (D + 1) + (size_t)bq * c.H * (D + c.r + 2)) * 4 > 200 * 1024) bq >>= 1;
+  while (bq > 1 && ((size_t)kLatTile * (D + 1 + kLatWarps) + (size_t)bq * c.H * (D + c.r + 2)) * 4 > 200 * 1024) bq >>= 1;
   return bq;
 }
 
@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
   float *acc = qs + (size_t)pairs * D;             // [pairs][r]
   float *mx = acc + (size_t)pairs * r;             // [pairs]
   float *dn = mx + pairs;                          // [pairs]
+  float *prs = dn + pairs;                         // [warps][32]
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   const int slot = sp.slot[tok0];
   const int last_pos = sp.pos[tok0 + nq - 1];
@@ -234,9 +235,12 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
       const float corr = expf(m_old - m_new);
       const float psum = warp_sum(pr);
       float *a = acc + (size_t)p * r;
+      float *pw = prs + w * kLatTile;  // the tile's weights of this pair: lanes own coordinates below, so every lane reads all
+      pw[l] = pr;
+      __syncwarp();
       for (int j = l; j < r; j += 32) {
         float v = a[j] * corr;
-        for (int kk = 0; kk < nk; kk++) v = fmaf(__shfl_sync(0xffffffffu, pr, kk), tile[(size_t)kk * DP + j], v);
+        for (int kk = 0; kk < nk; kk++) v = fmaf(pw[kk], tile[(size_t)kk * DP + j], v);
         a[j] = v;
       }
       __syncwarp();
@@ -254,7 +258,7 @@ cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32
   if (n_qb <= 0) return cudaSuccess;
   if (c.r > kLatMaxR) return cudaErrorInvalidValue;
   const int D = c.r + c.dr, bq = stack_latent_block_tokens(c);
-  const size_t sh = ((size_t)kLatTile * (D + 1) + (size_t)bq * c.H * (D + c.r + 2)) * sizeof(float);
+  const size_t sh = ((size_t)kLatTile * (D + 1 + kLatWarps) + (size_t)bq * c.H * (D + c.r + 2)) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
   static DeviceOnce once;
   DIS_CUDA_TRY(once.run([&] {

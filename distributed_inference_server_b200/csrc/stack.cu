@@ -121,7 +121,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       L.g_off = L.dkv_off + (lc.kv_from < 0 ? lc.kv_rank + lc.rot_dim : 0);
       L.n_in = L.g_off + lc.heads * lc.vdim;
       StackLatent sl{lc.heads, lc.dim, lc.rot_dim, lc.vdim, lc.kv_rank, lc.rot_dims, lc.rot_base, lc.scale, sc->norm_eps};
-      if (((size_t)32 * (lc.kv_rank + lc.rot_dim + 1) + (size_t)lc.heads * (2 * lc.kv_rank + lc.rot_dim + 2)) * 4 > 200 * 1024)
+      if (((size_t)32 * (lc.kv_rank + lc.rot_dim + 9) + (size_t)lc.heads * (2 * lc.kv_rank + lc.rot_dim + 2)) * 4 > 200 * 1024)
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "heads * kv_rank does not fit shared memory");
       stack_bq = std::min(stack_bq, stack_latent_block_tokens(sl));
     } else return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown mixer");

@@ -1,0 +1,62 @@
+"""bin/trace_run end to end: a model folder written by the test, a schedule with portions beside single tokens, four state
+slots and a page pool smaller than the sum of the requests, logits compared with the plain implementation."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from tests import _stack_util as U
+from tests.test_stack_cpu import write_safetensors
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", None)])
+def test_trace_replay_matches_the_plain_implementation(tmp_path, dtype, tol):
+    cfg = U.config([(U.latent(), U.dense()), (U.lightning(), U.moe()), (U.latent(kv_from=0), None), (U.mingru(), U.dense())], vocab=90, width=40)
+    W = U.weights(cfg, seed=3)
+    model = tmp_path / "model"
+    model.mkdir()
+    (model / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(model / "model.safetensors", W)
+    rng = np.random.default_rng(4)
+    reqs = {k: rng.integers(0, 90, n).tolist() for k, n in [("a", 150), ("b", 70), ("c", 1), ("d", 64), ("e", 129), ("f", 40)]}
+    want = {k: U.oracle_logits(cfg, W, v) for k, v in reqs.items()}
+    # steps: (id, count) lists; at most four requests live, 320 tokens of pages (64 each) for 454 tokens in total
+    plan = [[("a", 100), ("b", 2)], [("a", 1), ("b", 60), ("c", 1)], [("a", 1), ("b", 1), ("d", 64)], [("a", 48), ("b", 7), ("d", 0)],
+            [("e", 3), ("f", 39)], [("e", 2), ("f", 1)], [("e", 124)]]
+    at, lines, asked = {k: 0 for k in reqs}, [], []
+    for n, st in enumerate(plan):
+        entries, end = [], []
+        for k, cnt in st:
+            if cnt == 0:
+                continue
+            lo, hi = at[k], at[k] + cnt
+            w = sorted(set(rng.integers(0, cnt, min(cnt, 5)).tolist() + [cnt - 1]))
+            entries.append({"id": k, "tokens": reqs[k][lo:hi], "want": w})
+            asked.append((n, [(k, lo + j) for j in w]))
+            at[k] = hi
+            if hi == len(reqs[k]):
+                end.append(k)
+        lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "320"], input="\n".join(lines) + "\n", capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == [f"done {n}" for n in range(len(plan))]
+    per_step = {}
+    for n, rows in asked:
+        per_step.setdefault(n, []).extend(rows)
+    got_all, want_all = [], []
+    for n, rows in per_step.items():
+        got = np.fromfile(out / f"{n}.f32", "<f4").reshape(len(rows), 90)
+        got_all.append(got)
+        want_all.append(np.stack([want[k][p] for k, p in rows]))
+    got_all, want_all = np.concatenate(got_all), np.concatenate(want_all)
+    if tol is not None:
+        assert U.rel_err(got_all, want_all) < tol
+    else:
+        assert U.bf16_close(got_all, want_all)
