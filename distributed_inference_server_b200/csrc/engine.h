@@ -4,6 +4,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/dis_engine.h"
@@ -165,6 +166,9 @@ struct Engine {
   struct StackTarget { StackTensor *dst; size_t off; std::vector<int64_t> shape; int transform; bool loaded; int layer; };
   std::map<std::string, StackTarget> stack_names;
   int stack_bq = 8;
+  bool stack_tc = true;  // bf16 dense projections on the tcgen05 GEMM (DIS_STACK_TC=0: the fp32-FMA product everywhere, A/B runs)
+  std::map<std::tuple<const void *, uint64_t, uint64_t, uint32_t>, TmaMap> stack_maps;  // (base, rows, cols, box rows)
+  const TmaMap *stack_map(const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
   int init_stack(const dis_engine_config *c, const dis_stack_config *sc);
   int load_named(const char *name, const void *host, int dtype, const int64_t *shape, int ndim);
   int stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t *out_tokens, int *out_finish, int *out_produced);

@@ -81,6 +81,22 @@ cudaError_t launch_stack_gemm(const StackGemm &g, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+__global__ void stack_sum_bias_kernel(const float *part, int n_part, long long stride, const float *bias, float *out, long long n,
+                                      int N) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float s = bias ? bias[i % N] : 0.f;
+    for (int k = 0; k < n_part; k++) s += part[(long long)k * stride + i];
+    out[i] = s;
+  }
+}
+cudaError_t launch_stack_sum_bias(const float *part, int n_part, long long stride, const float *bias, float *out, int M, int N,
+                                  cudaStream_t st) {
+  const long long n = (long long)M * N;
+  if (n <= 0) return cudaSuccess;
+  stack_sum_bias_kernel<<<(int)std::min<long long>((n + 255) / 256, 148 * 8), 256, 0, st>>>(part, n_part, stride, bias, out, n, N);
+  return cudaGetLastError();
+}
+
 // ------------------------------------------------------------------------------------------------ embedding, norms
 template <bool F32>
 __global__ void stack_embed_kernel(const void *embed, const uint32_t *tokens, float *x, int W) {

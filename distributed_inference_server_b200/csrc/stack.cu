@@ -41,6 +41,15 @@ void Engine::free_stack() {
   }
 }
 
+const TmaMap *Engine::stack_map(const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  const auto key = std::make_tuple(base, rows, cols, box_rows);
+  auto it = stack_maps.find(key);
+  if (it != stack_maps.end()) return &it->second;
+  TmaMap m;
+  if (make_tma_map_2d(&m, base, rows, cols, box_rows) != cudaSuccess) return nullptr;
+  return &stack_maps.emplace(key, m).first->second;
+}
+
 cudaError_t Engine::stack_meta(StepMeta &s, int cap_t, int cap_rows) {
   s.cap_tokens = cap_t;
   s.cap_rows = cap_rows;
@@ -88,7 +97,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   M.layers.resize((size_t)sc->n_layers);
   const int W = sc->width, taps = sc->canon_taps;
   // ---- configuration checks, per layer
-  bool any_latent = false;
+
   for (int i = 0; i < sc->n_layers; i++) {
     StackLayer &L = M.layers[(size_t)i];
     L.c = sc->layers[i];
@@ -108,7 +117,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       if (lc.heads <= 0 || lc.dim <= 0 || lc.vdim <= 0 || lc.kv_rank <= 0 || lc.rot_dim < 0 || lc.rot_dims < 0 || lc.rot_dims > lc.rot_dim || (lc.rot_dims & 1))
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "latent attention needs heads, dim, vdim, kv_rank, and an even rot_dims <= rot_dim");
       if (lc.kv_rank > 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_rank above 1024");
-      any_latent = true;
+
       if (lc.kv_from >= 0) {
         if (lc.kv_from >= i) return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name an earlier layer");
         const dis_layer_config &src = M.layers[(size_t)lc.kv_from].c;
@@ -313,6 +322,11 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.qf), cap * max_qf * 4));
   ENG_CUDA(alloc(&M.act, cap * max_act * esz));
   ENG_CUDA(alloc(&M.xr, (size_t)M.max_rows * W * esz));
+  if (const char *g = getenv("DIS_STACK_TC")) stack_tc = atoi(g) != 0;
+  if (!M.f32 && stack_tc) {
+    M.scratch_elems = 2 * cap * std::max(max_proj, (size_t)W);
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.scratch), M.scratch_elems * 4));
+  }
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.logits), (size_t)M.max_rows * sc->vocab * 4));
   logits = nullptr;  // the Llama buffer is not allocated; last_logits reads stack->logits
   if (max_top > 0) {
@@ -353,7 +367,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     stack_allocs.pop_back();  // freed with the engine's own buffers
     ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_page_table), (size_t)max_batch * max_pages * sizeof(int)));
     memset(h_page_table, 0, (size_t)max_batch * max_pages * sizeof(int));
-    (void)any_latent;
+
   }
   seqs.resize((size_t)max_batch);
   slot_stamp.assign((size_t)max_batch, 0);
@@ -566,8 +580,25 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   StackSpans sp{mt.d<uint32_t>(mt.o_tokens), mt.d<int>(mt.o_pos), mt.d<int>(mt.o_ptrow), mt.d<int>(mt.o_span),
                 mt.d<int>(mt.o_qb_tok0), mt.d<int>(mt.o_qb_len), mt.d<int>(mt.o_qb_pos0), mt.d<int>(mt.o_qb_ptrow), T, n_spans};
   uint64_t &kl = kernel_launches;
+  pdl_enabled() = false;  // this family's kernels are plain launches: every kernel starts after the one before it has ended
+  // Dense projection out[Mrows][N] = A[Mrows][K] W[N][K]^T (+ bias).  bf16 operands go to the tcgen05 product the Llama path
+  // uses (fp32 accumulation in TMEM; split-K slices summed, with the bias, by one more kernel); float operands, and shapes a
+  // TMA map cannot describe (K not a multiple of 8), to the fp32-FMA product.  a_rows: rows the buffer behind A holds.
   auto gemm = [&](const void *A, bool a_f32, long long lda, const StackTensor &Wt, size_t w_off, const float *bias, float *out,
-                  int Mrows, int N, int K) -> cudaError_t {
+                  int Mrows, int N, int K, int a_rows = 0) -> cudaError_t {
+    if (stack_tc && !f32 && !a_f32 && !Wt.f32 && a_rows > 0 && K % 8 == 0 && lda == K && (w_off * 2) % 16 == 0) {
+      const TmaMap *xm = stack_map(A, (uint64_t)a_rows, (uint64_t)K, (uint32_t)gemm_token_tile(Mrows));
+      const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(Wt.ptr) + w_off, (uint64_t)N, (uint64_t)K, 128);
+      if (!xm || !wm) return cudaErrorInvalidValue;
+      int s = gemm_pick_split_k(Mrows, N, K);
+      if ((size_t)s * Mrows * N > M.scratch_elems) s = 1;
+      kl++;
+      if (s == 1 && !bias) return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, stream);
+      if ((size_t)s * Mrows * N > M.scratch_elems) return cudaErrorInvalidValue;
+      RET_CUDA(launch_gemm_partial(*wm, *xm, M.scratch, Mrows, N, K, 0, s, stream));
+      kl++;
+      return launch_stack_sum_bias(M.scratch, s, (long long)Mrows * N, bias, out, Mrows, N, stream);
+    }
     StackGemm g;
     g.A = A; g.a_f32 = a_f32; g.lda = lda;
     g.W = Wt.f32 ? (const void *)(reinterpret_cast<const float *>(Wt.ptr) + w_off) : (const void *)(reinterpret_cast<const uint16_t *>(Wt.ptr) + w_off);
@@ -590,7 +621,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     const dis_layer_config &lc = L.c;
     RET_CUDA(sublayer_in(L.g4 + 0, L.canon1, L.cstate1));
     const int N = L.n_in;
-    RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W));
+    RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W, cap_tokens));
     int n_mix = 0;
     if (lc.mixer == DIS_MIX_LIGHTNING) {
       const int H = lc.heads, d = lc.dim, dv = lc.vdim;
@@ -627,15 +658,15 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       kl += 5;
       n_mix = H * dv;
     }
-    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, nullptr, M.y, T, W, n_mix));
+    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, nullptr, M.y, T, W, n_mix, cap_tokens));
     pend_y = M.y; pend_post = L.g4 + 1;
     if (lc.mlp == DIS_MLP_NONE) continue;
     RET_CUDA(sublayer_in(L.g4 + 2, L.canon2, L.cstate2));
     if (lc.mlp == DIS_MLP_DENSE) {
       const int ff = lc.ff;
-      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W));
+      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens));
       RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, T, ff, lc.limit, stream)); kl++;
-      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff));
+      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
       RET_CUDA(launch_stack_route(M.hc, f32, reinterpret_cast<const float *>(L.router.ptr), T, W, E, top, M.r_idx, M.r_wt, stream));
@@ -663,7 +694,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++;
   if (R <= 0) return cudaSuccess;
   RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream)); kl++;
-  RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W));
+  RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W, M.max_rows));
   const float *temp = mt.d<float>(mt.o_temp), *topp = mt.d<float>(mt.o_topp);
   const unsigned long long *seed = mt.d<unsigned long long>(mt.o_seed), *step = mt.d<unsigned long long>(mt.o_step);
   float *d_logprob = reinterpret_cast<float *>(M.d_out + M.max_rows);

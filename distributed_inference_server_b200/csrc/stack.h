@@ -91,6 +91,9 @@ cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const 
                                      cudaStream_t st);
 cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const float *g, void *out, bool f32, int R, int W, float eps,
                                     cudaStream_t st);
+// out[m][n] = bias[n] + sum_s part[s][m][n]: the split-K slices of a tensor-core product, with the projection's bias
+cudaError_t launch_stack_sum_bias(const float *part, int n_part, long long stride, const float *bias, float *out, int M, int N,
+                                  cudaStream_t st);
 constexpr int kStackGemmTile = 64;
 
 // ---- the model
@@ -137,6 +140,8 @@ struct StackModel {
   // activations
   float *x = nullptr, *y = nullptr, *hn = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *qf = nullptr, *logits = nullptr;
   void *hc = nullptr, *act = nullptr, *xr = nullptr;
+  float *scratch = nullptr;  // split-K slices of the tensor-core products
+  size_t scratch_elems = 0;
   // experts
   int *r_idx = nullptr, *counts = nullptr, *perm_tok = nullptr, *where = nullptr, *tiles = nullptr;
   float *r_wt = nullptr, *rows_out = nullptr;
