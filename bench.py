@@ -742,6 +742,100 @@ def run_prefix(args):
     return 0
 
 
+def run_kidolorn(args):
+    """Prefill and decode throughput of the layer-list family (Kidolorn) beside the Llama decoder at equal width, depth, feed-
+    forward size and vocabulary, random weights, one GPU.  Per size: one pass over `batch` prompts of `prompt_len` tokens
+    (prefill, tokens/s) and K decode steps of the same batch (tokens/s), both timed by the engine's CUDA events around the
+    pass (metadata upload and token read-back included).  Weights exceed L2 at every size, so no flush is needed."""
+    from distributed_inference_server_b200 import Engine, InferenceParams, ModelShape, WorkerConfig, models
+    from distributed_inference_server_b200.binding import FLAG_NO_GRAPH as B_FLAG_NO_GRAPH
+    sizes = {"w1024": (1024, 4096, 1024), "w2048": (2048, 8192, 2048)}
+    want = [k for k in (args.sizes.split(",") if args.sizes else sizes) if k in sizes]
+    batch, plen, vocab = args.batch or 8, args.prompt_len, 32000
+    rng = np.random.default_rng(0)
+    out = []
+    for key in want:
+        W, ff, eff = sizes[key]
+        H = W // 128
+
+        def lat(kv_from=None):
+            mx = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "rot": {"base": 10000.0, "dims": 64},
+                  "scale": 192 ** -0.5}
+            if kv_from is not None:
+                mx["kv_from"] = kv_from
+            return {"type": "latent_attention", "mixer": mx}
+        dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+        moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+        kinds = {"lightning": {"type": "lightning", "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": [0.99] * H}},
+                 "latent": lat(), "mingru": {"type": "mingru", "mixer": {"width": W}}}
+        variants = {"mixed": [("lightning", dense), ("latent", moe), ("latent_shared", dense), ("mingru", moe)]}
+        if args.per_mixer:
+            variants.update({m: [(m, dense)] * 4 for m in kinds})
+            variants["latent_moe"] = [("latent", moe)] * 4
+        rec = {"size": key, "width": W, "layers": 4, "ff": ff, "vocab": vocab, "batch": batch, "prompt_len": plen}
+        prompts = [rng.integers(0, vocab, plen).tolist() for _ in range(batch)]
+        P = InferenceParams(max_tokens=1 << 20, temperature=0.0)
+
+        def measure(eng):
+            slots = [eng.seq_add(p, P) for p in prompts]
+            t_pre = []
+            # prefill: the whole batch in one pass; repeated on fresh sequences for the timed runs
+            for it in range(1 + max(1, args.ttft_runs)):
+                if it:
+                    for sl in slots:
+                        eng.seq_remove(sl)
+                    slots = [eng.seq_add(p, P) for p in prompts]
+                eng.step(slots, batch * plen)
+                t_pre.append(eng.status().last_step_ms)
+            for _ in range(args.warmup):
+                eng.decode(slots)
+            k0 = eng.status().kernel_launches
+            ms = 0.0
+            for _ in range(args.steps):
+                eng.decode(slots)
+                ms += eng.status().last_step_ms
+            launches = eng.status().kernel_launches - k0
+            for sl in slots:
+                eng.seq_remove(sl)
+            pre = min(t_pre[1:])
+            return {"prefill_ms": round(pre, 3), "prefill_tokens_per_s": round(batch * plen / pre * 1e3, 1),
+                    "decode_ms_per_step": round(ms / args.steps, 4), "decode_tokens_per_s": round(batch * args.steps / ms * 1e3, 1),
+                    "launches_per_decode_step": launches // max(1, args.steps)}
+        for vname, layers in variants.items():
+            cfg = {"architecture": "Kidolorn", "vocab": vocab, "width": W, "canon": {"taps": 4}, "norm": {"eps": 1e-5}, "layers": []}
+            first_latent = None
+            for i, (m, mlp) in enumerate(layers):
+                if m == "latent_shared":
+                    ly = lat(first_latent)
+                else:
+                    ly = json.loads(json.dumps(kinds[m]))
+                    if m == "latent" and first_latent is None:
+                        first_latent = i
+                cfg["layers"].append(dict(ly, mlp=mlp))
+            spec = models.kidolorn_spec(cfg)
+            pool = batch * (plen + args.steps + args.warmup + 64)
+            eng = Engine(WorkerConfig(None, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(pool + 63) // 64,
+                                      stack=spec, context_size=plen + args.steps + args.warmup + 64, compute_dtype="bfloat16",
+                                      flags=B_FLAG_NO_GRAPH if args.no_graph else 0))
+            for name, a in models.random_tensors(spec, seed=1).items():
+                eng.load_named(name, a)
+            eng.finalize()
+            rec["kidolorn_" + vname] = measure(eng)
+            eng.close()
+        shape = ModelShape(vocab, W, 4, H, max(1, H // 4), 128, ff, plen + args.steps + args.warmup + 64)
+        eng = Engine(WorkerConfig(shape, max_batch=batch, max_step_tokens=batch * plen, page_size=64,
+                                  kv_pages=(batch * (plen + args.steps + args.warmup + 64) + 63) // 64 + batch))
+        eng.load_synthetic(1)
+        eng.finalize()
+        rec["llama"] = measure(eng)
+        eng.close()
+        out.append(rec)
+    line = {"metric": "kidolorn_vs_llama_equal_size", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random tokens)", "higher_is_better": True, "sizes": out}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -760,7 +854,9 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="TP: use NCCL instead of the fused peer-memory exchange (A/B)")
     ap.add_argument("--tp-exchange", choices=["auto", "oneshot", "twoshot", "ll", "wide"], default="auto",
                     help="TP: peer-memory exchange kernel (auto = ll, the flag-in-data row kernel, up to hidden 4096; wide, the same protocol on a (row, column block) grid, above)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn = the layer-list family beside Llama at equal size")
+    ap.add_argument("--sizes", default="", help="kidolorn: comma list out of w1024,w2048 (default both)")
+    ap.add_argument("--per-mixer", action="store_true", help="kidolorn: also four layers of each mixer alone")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b = BASELINE configs[3] (TP=8, batch 32)")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--prefill-budget", type=int, default=0, help="serving: prompt tokens read per scheduler step (0 = library default)")
@@ -778,6 +874,8 @@ def main():
         return run_prefix(args)
     if args.workload == "serving":
         return run_serving(args)
+    if args.workload == "kidolorn":
+        return run_kidolorn(args)
     return run_ours(args)
 
 

@@ -341,7 +341,7 @@ Engine::~Engine() {
   if (cfg.device >= 0) cudaSetDevice(cfg.device);
   if (stream) cudaStreamSynchronize(stream);
   free_stack();
-  for (auto &g : graphs) cudaGraphExecDestroy(g.second);
+  for (auto &g : graphs) if (g.second) cudaGraphExecDestroy(g.second);
   for (auto ev : prof_events) cudaEventDestroy(ev);
   if (comm && nccl) nccl->CommDestroy(comm);
   for (int r = 0; r < kTpMaxRanks; r++) if (peer_base[r]) cudaIpcCloseMemHandle(peer_base[r]);

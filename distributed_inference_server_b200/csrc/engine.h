@@ -166,6 +166,12 @@ struct Engine {
   struct StackTarget { StackTensor *dst; size_t off; std::vector<int64_t> shape; int transform; bool loaded; int layer; };
   std::map<std::string, StackTarget> stack_names;
   int stack_bq = 8;
+  struct StackSpanH { int tok0, len, pos0, slot; bool products; };
+  std::vector<StackSpanH> stack_spans_h;  // spans of the pass being built; products: its latent attention runs as matrix products
+  int stack_lat_split = 1, stack_lat_keys = 0;  // slicing of the history in latent attention for the pass being built
+  int stack_lat_heads = 0;    // most heads of a latent layer
+  int stack_max_ctx = 0;      // longest history (tokens in the cache after the pass) among the sequences of the pass being built
+  size_t stack_lat_rec = 0;   // floats of one token's slice record in split latent attention: max over layers of heads * (kv_rank + 2)
   bool stack_tc = true;  // bf16 dense projections on the tcgen05 GEMM (DIS_STACK_TC=0: the fp32-FMA product everywhere, A/B runs)
   std::map<std::tuple<const void *, uint64_t, uint64_t, uint32_t>, TmaMap> stack_maps;  // (base, rows, cols, box rows)
   const TmaMap *stack_map(const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);

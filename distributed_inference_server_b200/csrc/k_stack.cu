@@ -290,13 +290,13 @@ cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, in
   return cudaGetLastError();
 }
 
-// Rows of the experts' matrices: the (token, choice) pairs sorted by expert, every expert's rows padded to whole row tiles in
-// the tile list only (the row space itself is dense).  One block; tokens are walked in order, so a pair's row is a function of
-// the routing alone.
+// Rows of the experts' matrices: the (token, choice) pairs grouped by expert, every expert's rows padded to whole row tiles in
+// the tile list only (the row space itself is dense).  One block.  Inside an expert's range the pairs land in the order their
+// threads arrive; a row's result does not depend on where in the range it lies, so the values are the same run to run.
 __global__ void stack_moe_plan_kernel(const int *idx, int n, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
                                       int *tiles, int max_tiles) {
-  extern __shared__ int sh[];  // [E] counts, [E] offsets
-  int *cnt = sh, *off = sh + E;
+  extern __shared__ int sh[];  // [E] counts, [E] cursors
+  int *cnt = sh, *cur = sh + E;
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
@@ -304,7 +304,7 @@ __global__ void stack_moe_plan_kernel(const int *idx, int n, int top, int E, int
   if (threadIdx.x == 0) {
     int o = 0, nt = 0;
     for (int e = 0; e < E; e++) {
-      off[e] = o;
+      cur[e] = o;
       for (int r = 0; r < cnt[e] && nt < max_tiles; r += tile_rows) {
         tiles[1 + 3 * nt] = e; tiles[2 + 3 * nt] = o + r; tiles[3 + 3 * nt] = min(tile_rows, cnt[e] - r);
         nt++;
@@ -315,16 +315,15 @@ __global__ void stack_moe_plan_kernel(const int *idx, int n, int top, int E, int
     tiles[0] = nt;
   }
   __syncthreads();
-  // one thread per expert walks the pairs in order: stable, no atomics on the positions
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int o = off[e];
-    for (int i = 0; i < n; i++)
-      if (idx[i] == e) { perm_tok[o] = i / top; where[i] = o; o++; }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int o = atomicAdd(&cur[idx[i]], 1);
+    perm_tok[o] = i / top;
+    where[i] = o;
   }
 }
 cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
                                   int *tiles, int max_tiles, cudaStream_t st) {
-  stack_moe_plan_kernel<<<1, 256, (size_t)2 * E * sizeof(int), st>>>(idx, T * top, top, E, tile_rows, counts, perm_tok, where, tiles,
+  stack_moe_plan_kernel<<<1, 1024, (size_t)2 * E * sizeof(int), st>>>(idx, T * top, top, E, tile_rows, counts, perm_tok, where, tiles,
                                                                       max_tiles);
   return cudaGetLastError();
 }

@@ -192,7 +192,7 @@ template <bool F32>
 __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const float *qf, const void *pool, const float *sink,
                                                                            StackLatent c, StackSpans sp, const int *qb_tok0,
                                                                            const int *qb_len, const int *page_table, int max_pages,
-                                                                           int page_size, float *ol) {
+                                                                           int page_size, float *ol, int keys_per_split, float *part) {
   extern __shared__ float shm[];
   const int D = c.r + c.dr, DP = D + 1, r = c.r;
   const int tok0 = qb_tok0[blockIdx.x], nq = qb_len[blockIdx.x];
@@ -208,15 +208,35 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
   const int last_pos = sp.pos[tok0 + nq - 1];
   for (int i = threadIdx.x; i < pairs * D; i += blockDim.x) qs[i] = qf[(long long)tok0 * c.H * D + i];
   for (int i = threadIdx.x; i < pairs * r; i += blockDim.x) acc[i] = 0.f;
-  for (int i = threadIdx.x; i < pairs; i += blockDim.x) { mx[i] = sink[i % c.H]; dn[i] = 1.f; }
+  // the whole history in one CTA: the running maximum starts at the head's sink and the denominator at exp(sink - max) = 1;
+  // one slice of the history (blockIdx.y, keys_per_split keys): both start empty and the sink joins when the slices are merged
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) { mx[i] = part ? -INFINITY : sink[i % c.H]; dn[i] = part ? 0.f : 1.f; }
   const int *pt = page_table + (long long)slot * max_pages;
-  for (int k0 = 0; k0 <= last_pos; k0 += kLatTile) {
-    const int nk = min(kLatTile, last_pos + 1 - k0);
+  const int k_begin = part ? (int)blockIdx.y * keys_per_split : 0;
+  const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
+  for (int k0 = k_begin; k0 < k_end; k0 += kLatTile) {
+    const int nk = min(kLatTile, k_end - k0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nk * D; i += blockDim.x) {
-      const int kk = i / D, cc = i % D, kp = k0 + kk;
-      const long long prow = (long long)pt[kp / page_size] * page_size + kp % page_size;
-      tile[(size_t)kk * DP + cc] = ld_el<F32>(pool, prow * D + cc);
+    if (!F32 && (D & 7) == 0) {  // a row of the pool is D bf16 values, 16-byte aligned: eight per load
+      const int vpr = D >> 3;
+      for (int i = threadIdx.x; i < nk * vpr; i += blockDim.x) {
+        const int kk = i / vpr, cv = i - kk * vpr, kp = k0 + kk;
+        const long long prow = (long long)pt[kp / page_size] * page_size + kp % page_size;
+        const uint4 v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(pool) + prow * D + cv * 8);
+        float *dst = tile + (size_t)kk * DP + cv * 8;
+        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          dst[2 * j] = __uint_as_float(w4[j] << 16);
+          dst[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < nk * D; i += blockDim.x) {
+        const int kk = i / D, cc = i % D, kp = k0 + kk;
+        const long long prow = (long long)pt[kp / page_size] * page_size + kp % page_size;
+        tile[(size_t)kk * DP + cc] = ld_el<F32>(pool, prow * D + cc);
+      }
     }
     __syncthreads();
     for (int p = w; p < pairs; p += kLatWarps) {
@@ -232,7 +252,7 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
       const float m_old = mx[p];
       const float m_new = fmaxf(m_old, warp_max(sc));
       const float pr = sc == -INFINITY ? 0.f : expf(sc - m_new);
-      const float corr = expf(m_old - m_new);
+      const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
       const float psum = warp_sum(pr);
       float *a = acc + (size_t)p * r;
       float *pw = prs + w * kLatTile;  // the tile's weights of this pair: lanes own coordinates below, so every lane reads all
@@ -249,14 +269,93 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < pairs * r; i += blockDim.x) ol[(long long)tok0 * c.H * r + i] = acc[i] / dn[i / r];
+  if (!part) {
+    for (int i = threadIdx.x; i < pairs * r; i += blockDim.x) ol[(long long)tok0 * c.H * r + i] = acc[i] / dn[i / r];
+    return;
+  }
+  // slice record per pair: r unnormalised sums, then the slice's maximum and denominator
+  float *rec = part + ((long long)blockIdx.y * sp.T * c.H + (long long)tok0 * c.H) * (r + 2);
+  for (int i = threadIdx.x; i < pairs * r; i += blockDim.x) rec[(long long)(i / r) * (r + 2) + i % r] = acc[i];
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) { rec[(long long)i * (r + 2) + r] = mx[i]; rec[(long long)i * (r + 2) + r + 1] = dn[i]; }
+}
+
+// Merge of the slices: out = sum_s acc_s e^(m_s - M) / (e^(sink - M) + sum_s l_s e^(m_s - M)), M = max(sink, max_s m_s).
+__global__ void stack_latent_merge_kernel(const float *part, const float *sink, int n_split, int pairs_total, int H, int r, float *ol) {
+  const int p = blockIdx.x;
+  const float sk = sink[p % H];
+  float M = sk;
+  for (int s = 0; s < n_split; s++) M = fmaxf(M, part[((long long)s * pairs_total + p) * (r + 2) + r]);
+  float den = expf(sk - M);
+  for (int s = 0; s < n_split; s++) {
+    const float *rec = part + ((long long)s * pairs_total + p) * (r + 2);
+    if (rec[r] != -INFINITY) den += rec[r + 1] * expf(rec[r] - M);
+  }
+  for (int j = threadIdx.x; j < r; j += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < n_split; s++) {
+      const float *rec = part + ((long long)s * pairs_total + p) * (r + 2);
+      if (rec[r] != -INFINITY) v = fmaf(rec[j], expf(rec[r] - M), v);
+    }
+    ol[(long long)p * r + j] = v / den;
+  }
+}
+
+// ---- latent attention of long prompt portions as matrix products (bf16 operands, fp32 accumulation): the sequence's latents
+// are copied out of their pages into one contiguous matrix and its transpose, scores = Q C^T and outputs = P C run on the
+// tensor-core product, and the kernel between them turns a block of score rows into softmax weights (fp32, causal, sink).
+__global__ void stack_latent_gather_kernel(const uint16_t *pool, const int *pt, int page_size, int D, int r, int ctx, int ctx8,
+                                           uint16_t *cg, uint16_t *cgt) {
+  const int kp = blockIdx.x;
+  const long long prow = kp < ctx ? (long long)pt[kp / page_size] * page_size + kp % page_size : 0;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    const uint16_t v = kp < ctx ? pool[prow * D + c] : (uint16_t)0;
+    cg[(long long)kp * D + c] = v;
+    if (c < r) cgt[(long long)c * ctx8 + kp] = v;
+  }
+}
+cudaError_t launch_stack_latent_gather(const void *pool, const int *pt_row, int page_size, int D, int r, int ctx, int ctx8,
+                                       uint16_t *cg, uint16_t *cgt, cudaStream_t st) {
+  stack_latent_gather_kernel<<<ctx8, 128, 0, st>>>(reinterpret_cast<const uint16_t *>(pool), pt_row, page_size, D, r, ctx, ctx8, cg, cgt);
+  return cudaGetLastError();
+}
+
+// Row (t, h) of S [rows][ld] holds the raw scores of the query at position pos_first + t against keys 0 .. ld-1.
+__global__ void __launch_bounds__(256) stack_latent_softmax_kernel(const float *S, int ld, const float *sink, int H, int pos_first,
+                                                                   float scale, uint16_t *P) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const int h = (int)(row % H), qpos = pos_first + (int)(row / H);
+  const float *s = S + row * ld;
+  const int nk = min(ld, qpos + 1);
+  const float sk = sink[h];
+  float m = sk;
+  for (int k = threadIdx.x; k < nk; k += blockDim.x) m = fmaxf(m, s[k] * scale);
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = m;
+  __syncthreads();
+  for (int i = 0; i < (int)(blockDim.x >> 5); i++) m = fmaxf(m, sh[i]);
+  float sum = 0.f;
+  for (int k = threadIdx.x; k < nk; k += blockDim.x) sum += expf(s[k] * scale - m);
+  sum = block_sum(sum, sh) + expf(sk - m);
+  const float inv = 1.f / sum;
+  uint16_t *p = P + row * ld;
+  for (int k = threadIdx.x; k < ld; k += blockDim.x) p[k] = k < nk ? float_to_bf16_bits(expf(s[k] * scale - m) * inv) : (uint16_t)0;
+}
+cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const float *sink, int H, int pos_first, float scale,
+                                        uint16_t *P, cudaStream_t st) {
+  if (rows <= 0) return cudaSuccess;
+  stack_latent_softmax_kernel<<<rows, 256, 0, st>>>(S, ld, sink, H, pos_first, scale, P);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32, const float *sink, const StackLatent &c,
                                      const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, const int *page_table,
-                                     int max_pages, int page_size, float *ol, cudaStream_t st) {
+                                     int max_pages, int page_size, float *ol, int n_split, int keys_per_split, float *part,
+                                     cudaStream_t st) {
   if (n_qb <= 0) return cudaSuccess;
   if (c.r > kLatMaxR) return cudaErrorInvalidValue;
+  if (n_split <= 1 || !part) { n_split = 1; part = nullptr; }
   const int D = c.r + c.dr, bq = stack_latent_block_tokens(c);
   const size_t sh = ((size_t)kLatTile * (D + 1 + kLatWarps) + (size_t)bq * c.H * (D + c.r + 2)) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
@@ -265,8 +364,10 @@ cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32
     cudaError_t e = cudaFuncSetAttribute(stack_latent_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_latent_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
   }));
-  if (f32) stack_latent_attn_kernel<true><<<n_qb, kLatWarps * 32, sh, st>>>(qf, pool, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol);
-  else stack_latent_attn_kernel<false><<<n_qb, kLatWarps * 32, sh, st>>>(qf, pool, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol);
+  const dim3 grid(n_qb, n_split);
+  if (f32) stack_latent_attn_kernel<true><<<grid, kLatWarps * 32, sh, st>>>(qf, pool, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol, keys_per_split, part);
+  else stack_latent_attn_kernel<false><<<grid, kLatWarps * 32, sh, st>>>(qf, pool, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol, keys_per_split, part);
+  if (part) stack_latent_merge_kernel<<<sp.T * c.H, 128, 0, st>>>(part, sink, n_split, sp.T * c.H, c.H, c.r, ol);
   return cudaGetLastError();
 }
 

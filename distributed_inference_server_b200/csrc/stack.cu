@@ -244,6 +244,8 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       max_mix = std::max(max_mix, (size_t)H * std::max(r, dv));
       max_act = std::max(max_act, (size_t)H * dv);
       max_qf = std::max(max_qf, (size_t)H * (r + dr));
+      stack_lat_rec = std::max(stack_lat_rec, (size_t)H * (r + 2));
+      stack_lat_heads = std::max(stack_lat_heads, H);
     }
     if (lc.mlp == DIS_MLP_DENSE) {
       const int ff = lc.ff;
@@ -322,6 +324,30 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.qf), cap * max_qf * 4));
   ENG_CUDA(alloc(&M.act, cap * max_act * esz));
   ENG_CUDA(alloc(&M.xr, (size_t)M.max_rows * W * esz));
+  if (stack_lat_rec && !M.f32 && stack_tc) {
+    bool ok = true;
+    size_t max_D = 0, max_r = 0;
+    for (auto &L : M.layers)
+      if (L.c.mixer == DIS_MIX_LATENT) {
+        ok = ok && (L.c.kv_rank % 8 == 0) && ((L.c.kv_rank + L.c.rot_dim) % 8 == 0);
+        max_D = std::max(max_D, (size_t)(L.c.kv_rank + L.c.rot_dim)); max_r = std::max(max_r, (size_t)L.c.kv_rank);
+      }
+    if (const char *g = getenv("DIS_STACK_LATENT_PRODUCTS")) ok = ok && atoi(g) != 0;
+    if (ok) {
+      M.lat_gemm = true;
+      M.lat_ctx_cap = (m.max_ctx + 7) / 8 * 8;
+      M.lat_s_elems = std::max((size_t)16 << 20, (size_t)64 * M.lat_ctx_cap);
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_qb), cap * max_qf * 2));
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_cg), (size_t)M.lat_ctx_cap * max_D * 2));
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_cgt), (size_t)M.lat_ctx_cap * max_r * 2));
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_s), M.lat_s_elems * 4));
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_p), M.lat_s_elems * 2));
+    }
+  }
+  if (stack_lat_rec) {
+    M.lat_part_elems = (size_t)2048 * stack_lat_rec;  // (tokens x slices) of one pass
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_part), M.lat_part_elems * 4));
+  }
   if (const char *g = getenv("DIS_STACK_TC")) stack_tc = atoi(g) != 0;
   if (!M.f32 && stack_tc) {
     M.scratch_elems = 2 * cap * std::max(max_proj, (size_t)W);
@@ -476,6 +502,8 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
   plan_mixed_step((int)idx.size(), rem.data(), max_prefill_tokens > 0 ? max_prefill_tokens : cap_tokens, cap_tokens, take.data());
   StepMeta &mt = meta_pre;
   int T = 0, R = 0, SP = 0, QB = 0;
+  stack_max_ctx = 0;
+  stack_spans_h.clear();
   bool all_greedy = true;
   // rows first: a pass that would produce more logits rows than the engine holds is refused before anything changes
   {
@@ -497,6 +525,7 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     if (tk <= 0) continue;
     if (rem[k] == 0) s.prompt.push_back(s.last_token);
     const int p0 = s.len;
+    stack_max_ctx = std::max(stack_max_ctx, p0 + tk);
     for (int j = 0; j < tk; j++) {
       mt.h<uint32_t>(mt.o_tokens)[T + j] = s.prompt[(size_t)(p0 + j)];
       mt.h<int>(mt.o_pos)[T + j] = p0 + j;
@@ -508,7 +537,10 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     mt.h<int>(mt.o_qb_pos0)[SP] = p0;
     mt.h<int>(mt.o_qb_ptrow)[SP] = slots[i];
     SP++;
-    for (int j = 0; j < tk; j += stack_bq) {
+    // long portions: latent attention as matrix products; short ones and decode rows: query blocks of the paged kernel
+    const bool products = M.lat_gemm && tk >= 32 && (size_t)stack_lat_heads * ((p0 + tk + 7) / 8 * 8) <= M.lat_s_elems;
+    stack_spans_h.push_back({T, tk, p0, slots[i], products});
+    for (int j = 0; j < tk && !products; j += stack_bq) {
       mt.h<int>(mt.o_ab_tok0)[QB] = T + j;
       mt.h<int>(mt.o_ab_len)[QB] = std::min(stack_bq, tk - j);
       QB++;
@@ -535,7 +567,54 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     pt_dirty = false;
   }
   ENG_CUDA(cudaMemcpyAsync(mt.dev, mt.host, mt.bytes, cudaMemcpyHostToDevice, stream));
-  ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));
+  // latent attention: with few query blocks the history is cut into slices so that about two CTAs per SM run
+  stack_lat_split = 1; stack_lat_keys = 0;
+  if (QB > 0 && QB < kNumSMs && stack_max_ctx >= 256 && stack_lat_rec) {
+    int sp = std::min(std::min((2 * kNumSMs + QB - 1) / QB, stack_max_ctx / 128), 64);
+    const int keys = ((stack_max_ctx + sp - 1) / sp + 31) / 32 * 32;
+    sp = (stack_max_ctx + keys - 1) / keys;
+    if (sp > 1 && (size_t)sp * T * stack_lat_rec <= M.lat_part_elems) { stack_lat_split = sp; stack_lat_keys = keys; }
+  }
+  // A pass of single tokens only (decode rows, no kept prompt positions) has the same launches whenever its size, its
+  // slicing and its sampler agree: the second such pass is captured into a CUDA graph and later ones replay it.
+  const bool graphable = !(cfg.flags & DIS_FLAG_NO_GRAPH) && T == SP && R == T && T <= 0xFFFF;
+  if (!graphable) {
+    ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));
+  } else {
+    const uint64_t key = (uint64_t)T | ((uint64_t)stack_lat_split << 16) | ((uint64_t)(stack_lat_keys / 32) << 24) | (all_greedy ? 1ull << 60 : 0ull);
+    auto it = graphs.find(key);
+    if (it != graphs.end() && it->second) {
+      ENG_CUDA(cudaGraphLaunch(it->second, stream));
+      kernel_launches += graph_launches[key];
+    } else if (it == graphs.end()) {
+      if (graphs.size() > 256) {  // histories that grow through many slicings: start over rather than keep every graph
+        for (auto &g : graphs) if (g.second) cudaGraphExecDestroy(g.second);
+        graphs.clear();
+      }
+      const uint64_t before = kernel_launches;
+      ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));  // first sight: plain launches (function attributes, tensor maps)
+      graph_launches[key] = kernel_launches - before;
+      graphs.emplace(key, nullptr);
+    } else {
+      const uint64_t before = kernel_launches;
+      cudaGraph_t g = nullptr;
+      ENG_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+      const cudaError_t e1 = stack_forward(T, SP, QB, R, all_greedy);
+      const cudaError_t e2 = cudaStreamEndCapture(stream, &g);
+      if (e1 != cudaSuccess || e2 != cudaSuccess || !g) {
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+        healthy = false;
+        return fail(DIS_ERR_INFERENCE_FAILED, std::string("decode graph capture failed: ") + cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+      }
+      cudaGraphExec_t ex = nullptr;
+      ENG_CUDA(cudaGraphInstantiate(&ex, g, 0));
+      cudaGraphDestroy(g);
+      kernel_launches = before + graph_launches[key];
+      it->second = ex;
+      ENG_CUDA(cudaGraphLaunch(ex, stream));
+    }
+  }
   if (R > 0) ENG_CUDA(cudaMemcpyAsync(M.h_out, M.d_out, (size_t)2 * M.max_rows * 4, cudaMemcpyDeviceToHost, stream));
   ENG_CUDA(cudaEventRecord(ev1, stream));
   ENG_CUDA(cudaEventSynchronize(ev1));
@@ -616,6 +695,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     kl++;
     return launch_stack_copy_act(M.hn, M.hc, f32, (long long)T * W, stream);
   };
+  const int lat_split = stack_lat_split, lat_keys = stack_lat_keys;
   for (size_t li = 0; li < M.layers.size(); li++) {
     StackLayer &L = M.layers[li];
     const dis_layer_config &lc = L.c;
@@ -646,7 +726,36 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       g.M = T; g.N = r; g.K = d; g.batch = H;
       RET_CUDA(launch_stack_gemm(g, stream));
       RET_CUDA(launch_stack_latent_attn(M.qf, KV.pool, f32, reinterpret_cast<const float *>(L.sink.ptr), sl, sp, mt.d<int>(mt.o_ab_tok0),
-                                        mt.d<int>(mt.o_ab_len), n_qb, d_page_table, max_pages, page_size, M.mix, stream));
+                                        mt.d<int>(mt.o_ab_len), n_qb, d_page_table, max_pages, page_size, M.mix, lat_split, lat_keys,
+                                        M.lat_part, stream));
+      if (lat_split > 1) kl++;
+      bool any_products = false;
+      for (auto &sh : stack_spans_h) any_products = any_products || sh.products;
+      if (any_products) {
+        RET_CUDA(launch_stack_copy_act(M.qf, M.lat_qb, false, (long long)T * H * D, stream)); kl++;
+        for (auto &sh : stack_spans_h) {
+          if (!sh.products) continue;
+          const int ctx = sh.pos0 + sh.len, ctx8 = (ctx + 7) / 8 * 8;
+          RET_CUDA(launch_stack_latent_gather(KV.pool, d_page_table + (size_t)sh.slot * max_pages, page_size, D, r, ctx, ctx8, M.lat_cg,
+                                              M.lat_cgt, stream));
+          kl++;
+          const int max_nq = (int)std::min<size_t>(M.lat_s_elems / ((size_t)H * ctx8), 4096);
+          for (int j = 0; j < sh.len; j += max_nq) {
+            const int nq = std::min(max_nq, sh.len - j), rows = nq * H;
+            const int nkeys = (sh.pos0 + j + nq + 7) / 8 * 8;  // keys the block's last query sees, rounded up (the rest are masked)
+            TmaMap qm, cm, pm, ctm;
+            RET_CUDA(make_tma_map_2d(&qm, M.lat_qb + (size_t)(sh.tok0 + j) * H * D, (uint64_t)rows, (uint64_t)D, (uint32_t)gemm_token_tile(rows)));
+            RET_CUDA(make_tma_map_2d(&cm, M.lat_cg, (uint64_t)nkeys, (uint64_t)D, 128));
+            RET_CUDA(launch_gemm_partial(cm, qm, M.lat_s, rows, nkeys, D, 0, 1, stream));
+            RET_CUDA(launch_stack_latent_softmax(M.lat_s, rows, nkeys, reinterpret_cast<const float *>(L.sink.ptr), H, sh.pos0 + j, sl.scale,
+                                                 M.lat_p, stream));
+            RET_CUDA(make_tma_map_2d(&pm, M.lat_p, (uint64_t)rows, (uint64_t)nkeys, (uint32_t)gemm_token_tile(rows)));
+            RET_CUDA(make_tma_map_2d(&ctm, M.lat_cgt, (uint64_t)r, (uint64_t)ctx8, 128));
+            RET_CUDA(launch_gemm_partial(ctm, pm, M.mix + (size_t)(sh.tok0 + j) * H * r, rows, r, nkeys, 0, 1, stream));
+            kl += 3;
+          }
+        }
+      }
       // values: mix2[t][h][0..dv) = sum_b ol[t][h][b] * uv[h*dv + .][b]
       StackGemm v;
       v.A = M.mix; v.a_f32 = true; v.lda = (long long)H * r; v.a_bs = r;

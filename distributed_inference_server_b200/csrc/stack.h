@@ -74,10 +74,19 @@ cudaError_t launch_stack_latent_prep(const float *proj, long long ld, int q_off,
                                      const int *page_table, int max_pages, int page_size, cudaStream_t st);
 // step 2: scores of qf against the pool rows of the sequence (causal, softmax with a per-head sink in the denominator),
 // output the weighted sum of the latents: ol [T][H][r] fp32.  qb_tok0 / qb_len: query blocks (tokens of one span).
+// n_split > 1: the history is cut into slices of keys_per_split keys (a multiple of 32), one CTA per (block, slice), whose
+// records ([n_split][T*H][r+2] floats in `part`) a second kernel merges -- few query blocks then still fill the GPU.
 int stack_latent_block_tokens(const StackLatent &c);
 cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32, const float *sink, const StackLatent &c,
                                      const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb,
-                                     const int *page_table, int max_pages, int page_size, float *ol, cudaStream_t st);
+                                     const int *page_table, int max_pages, int page_size, float *ol, int n_split,
+                                     int keys_per_split, float *part, cudaStream_t st);
+// Long prompt portions in bf16: latents of one sequence out of their pages into cg [ctx8][D] and cgt [r][ctx8] (rows / columns
+// from ctx to ctx8 zero), and softmax weights (bf16) from a block of raw score rows; the products between run on tcgen05.
+cudaError_t launch_stack_latent_gather(const void *pool, const int *pt_row, int page_size, int D, int r, int ctx, int ctx8,
+                                       uint16_t *cg, uint16_t *cgt, cudaStream_t st);
+cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const float *sink, int H, int pos_first, float scale,
+                                        uint16_t *P, cudaStream_t st);
 // act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu [M][2*ff] (gate | up)
 cudaError_t launch_stack_glu(const float *gu, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit, cudaStream_t st);
 // Router: logits in fp32 from hc and the fp32 router matrix; top-k by value (lowest index wins a tie); softmax over the chosen.
@@ -140,6 +149,14 @@ struct StackModel {
   // activations
   float *x = nullptr, *y = nullptr, *hn = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *qf = nullptr, *logits = nullptr;
   void *hc = nullptr, *act = nullptr, *xr = nullptr;
+  // latent attention of long portions as matrix products: bf16 queries, gathered latents and their transpose, score block, weights
+  bool lat_gemm = false;
+  int lat_ctx_cap = 0;
+  size_t lat_s_elems = 0;
+  uint16_t *lat_qb = nullptr, *lat_cg = nullptr, *lat_cgt = nullptr, *lat_p = nullptr;
+  float *lat_s = nullptr;
+  float *lat_part = nullptr;  // latent attention: slice records
+  size_t lat_part_elems = 0;
   float *scratch = nullptr;  // split-K slices of the tensor-core products
   size_t scratch_elems = 0;
   // experts

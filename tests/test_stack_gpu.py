@@ -23,6 +23,7 @@ MECHANISMS = {
     "mingru": [(U.mingru(), None)],
     "latent": [(U.latent(), None)],
     "latent_partial_rotation": [(U.latent(heads=3, dim=12, rot_dim=8, vdim=10, kv_rank=20, rot_dims=4, base=100.0), None)],
+    "latent_rows_of_16_bytes": [(U.latent(heads=2, dim=8, rot_dim=8, vdim=12, kv_rank=24), None)],
     "latent_shared": [(U.latent(), None), (U.mingru(), None), (U.latent(kv_from=0, vdim=20, dim=4, heads=3), None)],
     "dense": [(U.mingru(8), U.dense())],
     "moe": [(U.mingru(8), U.moe())],
@@ -95,6 +96,28 @@ def test_portions_of_several_sizes(sizes):
     e.close()
     assert U.rel_err(got, want) < F32_TOL
     assert U.rel_err(got, U.run_whole(cfg, W, t)) < SAME
+
+
+def test_long_portions_in_bfloat16_take_the_matrix_product_path():
+    """In bfloat16, latent attention of portions of 32 tokens or more runs as tensor-core products over latents gathered out of
+    their pages (kv_rank and kv_rank + rot_dim multiples of 8); shorter portions and single tokens run on the paged kernel.
+    Both must agree with the oracle, also when one sequence changes between them and when two sequences share a pass."""
+    cfg = U.config([(U.latent(heads=2, dim=8, rot_dim=8, vdim=16, kv_rank=24), U.dense()),
+                    (U.latent(heads=4, dim=16, rot_dim=8, vdim=8, kv_rank=24, kv_from=0), None)], width=64)
+    W = U.weights(cfg, seed=47)
+    a, b = toks(150, seed=31), toks(90, seed=32)
+    wa, wb = U.oracle_logits(cfg, W, a), U.oracle_logits(cfg, W, b)
+    e = U.engine(cfg, W, "bfloat16", pool_tokens=320, page_size=16)
+    f = U.Feeder(e)
+    f.step([("a", a, 40), ("b", b, 5)])
+    f.step([("a", a, 3), ("b", b, 64)])
+    f.step([("a", a, 64), ("b", b, 1)])
+    f.step([("a", a, 1), ("b", b, 20)])
+    f.step([("a", a, 42)])
+    ga, gb = f.end("a"), f.end("b")
+    e.close()
+    assert U.bf16_close(ga, wa) and U.bf16_close(gb, wb)
+    assert float(np.median(U.row_errs(ga, wa))) < 2e-2
 
 
 def test_batches_of_unequal_requests_against_each_alone():
