@@ -166,6 +166,7 @@ struct Engine {
   struct StackTarget { StackTensor *dst; size_t off; std::vector<int64_t> shape; int transform; bool loaded; int layer; };
   std::map<std::string, StackTarget> stack_names;
   int stack_bq = 8;
+  bool stack_capturing = false;  // a decode pass is being captured: nothing in it may wait for the device
   struct StackSpanH { int tok0, len, pos0, slot; bool products; };
   std::vector<StackSpanH> stack_spans_h;  // spans of the pass being built; products: its latent attention runs as matrix products
   int stack_lat_split = 1, stack_lat_keys = 0;  // slicing of the history in latent attention for the pass being built

@@ -328,6 +328,18 @@ cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int til
   return cudaGetLastError();
 }
 
+// rows of the expert row space, in bf16: row o = activation row perm_tok[o]
+__global__ void stack_moe_gather_kernel(const uint16_t *hc, const int *perm_tok, uint16_t *xs, int W) {
+  const long long o = blockIdx.x;
+  const uint16_t *src = hc + (long long)perm_tok[o] * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) xs[o * W + i] = src[i];
+}
+cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *xs, int rows, int W, cudaStream_t st) {
+  if (rows <= 0) return cudaSuccess;
+  stack_moe_gather_kernel<<<rows, 128, 0, st>>>(reinterpret_cast<const uint16_t *>(hc), perm_tok, reinterpret_cast<uint16_t *>(xs), W);
+  return cudaGetLastError();
+}
+
 __global__ void stack_moe_combine_kernel(const float *rows, const int *where, const float *wt, float *y, int W, int top) {
   const long long t = blockIdx.x;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {

@@ -35,6 +35,7 @@ void Engine::free_stack() {
   stack_allocs.clear();
   if (stack) {
     if (stack->h_out) cudaFreeHost(stack->h_out);
+    if (stack->h_counts) cudaFreeHost(stack->h_counts);
     for (StackTensor *v : stack->views) delete v;
     delete stack;
     stack = nullptr;
@@ -365,6 +366,10 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.where), rows * 4));
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.tiles), (size_t)(1 + 3 * M.max_tiles) * 4));
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.rows_out), rows * W * 4));
+    if (!M.f32 && stack_tc) {
+      ENG_CUDA(alloc(&M.moe_x, rows * W * 2));
+      ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&M.h_counts), (size_t)max_e * sizeof(int)));
+    }
   }
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.d_out), (size_t)2 * M.max_rows * 4));
   ENG_CUDA(cudaMallocHost(reinterpret_cast<void **>(&M.h_out), (size_t)2 * M.max_rows * 4));
@@ -599,7 +604,9 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
       const uint64_t before = kernel_launches;
       cudaGraph_t g = nullptr;
       ENG_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+      stack_capturing = true;
       const cudaError_t e1 = stack_forward(T, SP, QB, R, all_greedy);
+      stack_capturing = false;
       const cudaError_t e2 = cudaStreamEndCapture(stream, &g);
       if (e1 != cudaSuccess || e2 != cudaSuccess || !g) {
         if (g) cudaGraphDestroy(g);
@@ -780,6 +787,40 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
       RET_CUDA(launch_stack_route(M.hc, f32, reinterpret_cast<const float *>(L.router.ptr), T, W, E, top, M.r_idx, M.r_wt, stream));
       RET_CUDA(launch_stack_moe_plan(M.r_idx, T, top, E, kStackGemmTile, M.counts, M.perm_tok, M.where, M.tiles, M.max_tiles, stream));
+      // Large passes in bf16: one tensor-core product per expert over its rows.  The row counts come back to the host (one
+      // small copy and a wait), so this path is not taken while a decode pass is being captured into a graph.
+      if (M.moe_x && !stack_capturing && rows >= 64 * E && W % 8 == 0 && ff % 8 == 0) {
+        RET_CUDA(launch_stack_moe_gather(M.hc, M.perm_tok, M.moe_x, rows, W, stream));
+        RET_CUDA(cudaMemcpyAsync(M.h_counts, M.counts, (size_t)E * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        RET_CUDA(cudaStreamSynchronize(stream));
+        kl += 4;
+        int off = 0;
+        for (int e = 0; e < E; e++) {
+          const int cnt = M.h_counts[e];
+          if (cnt <= 0) continue;
+          TmaMap xm;
+          RET_CUDA(make_tma_map_2d(&xm, reinterpret_cast<uint16_t *>(M.moe_x) + (size_t)off * W, (uint64_t)cnt, (uint64_t)W, (uint32_t)gemm_token_tile(cnt)));
+          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.w_gu.ptr) + (size_t)e * 2 * ff * W, (uint64_t)2 * ff, (uint64_t)W, 128);
+          if (!wm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, stream));
+          off += cnt; kl++;
+        }
+        RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, rows, ff, lc.limit, stream));
+        off = 0;
+        for (int e = 0; e < E; e++) {
+          const int cnt = M.h_counts[e];
+          if (cnt <= 0) continue;
+          TmaMap xm;
+          RET_CUDA(make_tma_map_2d(&xm, reinterpret_cast<uint16_t *>(M.act) + (size_t)off * ff, (uint64_t)cnt, (uint64_t)ff, (uint32_t)gemm_token_tile(cnt)));
+          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.w_down.ptr) + (size_t)e * W * ff, (uint64_t)W, (uint64_t)ff, 128);
+          if (!wm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_partial(*wm, xm, M.rows_out + (size_t)off * W, cnt, W, ff, 0, 1, stream));
+          off += cnt; kl++;
+        }
+        RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, M.y, T, W, top, stream));
+        pend_y = M.y; pend_post = L.g4 + 3;
+        continue;
+      }
       const int tiles_cap = std::min(M.max_tiles, (rows + kStackGemmTile - 1) / kStackGemmTile + E);
       StackGemm g;
       g.A = M.hc; g.a_f32 = f32; g.lda = W; g.a_gather = M.perm_tok;

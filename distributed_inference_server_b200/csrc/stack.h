@@ -96,6 +96,7 @@ cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, in
 // tiles [1 + 3 * max_tiles], rows_total[1]
 cudaError_t launch_stack_moe_plan(const int *idx, int T, int top, int E, int tile_rows, int *counts, int *perm_tok, int *where,
                                   int *tiles, int max_tiles, cudaStream_t st);
+cudaError_t launch_stack_moe_gather(const void *hc, const int *perm_tok, void *xs, int rows, int W, cudaStream_t st);
 cudaError_t launch_stack_moe_combine(const float *rows, const int *where, const float *wt, float *y, int T, int W, int top,
                                      cudaStream_t st);
 cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const float *g, void *out, bool f32, int R, int W, float eps,
@@ -162,6 +163,8 @@ struct StackModel {
   // experts
   int *r_idx = nullptr, *counts = nullptr, *perm_tok = nullptr, *where = nullptr, *tiles = nullptr;
   float *r_wt = nullptr, *rows_out = nullptr;
+  void *moe_x = nullptr;       // bf16 activations in expert row order (per-expert tensor-core products of large passes)
+  int *h_counts = nullptr;     // pinned: rows per expert of the layer being run
   int max_tiles = 0;
   uint32_t *d_out = nullptr, *h_out = nullptr;  // [max_rows] ids then [max_rows] log-probabilities
 };

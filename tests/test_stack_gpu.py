@@ -120,6 +120,25 @@ def test_long_portions_in_bfloat16_take_the_matrix_product_path():
     assert float(np.median(U.row_errs(ga, wa))) < 2e-2
 
 
+@pytest.mark.parametrize("experts,top", [(2, 1), (4, 2), (3, 3)])
+def test_large_expert_passes_in_bfloat16_run_one_product_per_expert(experts, top):
+    """A pass with at least 64 rows per expert on average sorts its rows by expert and runs each expert's rows as one
+    tensor-core product; smaller passes (the single tokens after the prompt) use the grouped fp32-FMA product."""
+    cfg = U.config([(U.mingru(16), U.moe(ff=16, experts=experts, top=top)), (U.lightning(), U.moe(ff=24, experts=experts, top=top))])
+    W = U.weights(cfg, seed=53)
+    t = toks(260, seed=33)
+    want = U.oracle_logits(cfg, W, t)
+    e = U.engine(cfg, W, "bfloat16", pool_tokens=320, page_size=64)
+    f = U.Feeder(e)
+    f.step([("a", t, 250)])
+    for _ in range(10):
+        f.step([("a", t, 1)])
+    got = f.end("a")
+    e.close()
+    assert U.bf16_close(got, want)
+    assert float(np.median(U.row_errs(got, want))) < 2e-2
+
+
 def test_batches_of_unequal_requests_against_each_alone():
     cfg = U.config(FULL)
     W = U.weights(cfg, seed=13)
