@@ -55,9 +55,94 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
   for (int i = threadIdx.x; i < d * dv; i += blockDim.x) st[i] = S[i];
 }
 
+// The same recurrence with the state in registers: thread (warp w, lane l) owns S[w + 8 ii][l + 32 jj], ii < RI, jj < RJ, for the
+// whole span; q, k, v of eight tokens at a time are staged in shared memory (SiLU applied), so the span costs two barriers per
+// eight tokens and no shared-memory traffic for the state.  Sums run in the order of the kernel above.
+constexpr int kLightChunk = 8;
+template <int RI, int RJ>
+__global__ void __launch_bounds__(256) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, const float *decay,
+                                                                  float *state, StackSpans sp, float *__restrict__ o, int H, int d, int dv) {
+  extern __shared__ float shm[];
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  constexpr int nw = 8;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  float *qs = shm;                              // [chunk][d]
+  float *ks = qs + (size_t)kLightChunk * d;     // [chunk][d]
+  float *vs = ks + (size_t)kLightChunk * d;     // [chunk][dv]
+  float *part = vs + (size_t)kLightChunk * dv;  // [chunk][nw][dv]
+  float *st = state + ((long long)slot * H + h) * d * dv;
+  const float a = decay[h];
+  float S[RI][RJ];
+#pragma unroll
+  for (int ii = 0; ii < RI; ii++)
+#pragma unroll
+    for (int jj = 0; jj < RJ; jj++) {
+      const int i = w + ii * nw, j = l + jj * 32;
+      S[ii][jj] = (pos0 > 0 && i < d && j < dv) ? st[(size_t)i * dv + j] : 0.f;
+    }
+  const int per = 2 * d + dv;
+  for (int t0 = 0; t0 < len; t0 += kLightChunk) {
+    const int ct = min(kLightChunk, len - t0);
+    for (int e = threadIdx.x; e < ct * per; e += blockDim.x) {
+      const int t = e / per, c = e - t * per;
+      const float *row = proj + (long long)(tok0 + t0 + t) * ld;
+      if (c < d) qs[t * d + c] = silu_(row[(long long)h * d + c]);
+      else if (c < 2 * d) ks[t * d + c - d] = silu_(row[(long long)H * d + (long long)h * d + c - d]);
+      else vs[t * dv + c - 2 * d] = silu_(row[(long long)2 * H * d + (long long)h * dv + c - 2 * d]);
+    }
+    __syncthreads();
+    for (int t = 0; t < ct; t++) {
+      float vj[RJ], acc[RJ];
+#pragma unroll
+      for (int jj = 0; jj < RJ; jj++) { vj[jj] = l + jj * 32 < dv ? vs[t * dv + l + jj * 32] : 0.f; acc[jj] = 0.f; }
+#pragma unroll
+      for (int ii = 0; ii < RI; ii++) {
+        const int i = w + ii * nw;
+        if (i < d) {
+          const float ki = ks[t * d + i], qi = qs[t * d + i];
+#pragma unroll
+          for (int jj = 0; jj < RJ; jj++) {
+            S[ii][jj] = fmaf(a, S[ii][jj], ki * vj[jj]);
+            acc[jj] = fmaf(S[ii][jj], qi, acc[jj]);
+          }
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < RJ; jj++)
+        if (l + jj * 32 < dv) part[((size_t)t * nw + w) * dv + l + jj * 32] = acc[jj];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < ct * dv; e += blockDim.x) {
+      const int t = e / dv, j = e - t * dv;
+      float acc = 0.f;
+      for (int k = 0; k < nw; k++) acc += part[((size_t)t * nw + k) * dv + j];
+      o[(long long)(tok0 + t0 + t) * H * dv + (long long)h * dv + j] = acc;
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < RI; ii++)
+#pragma unroll
+    for (int jj = 0; jj < RJ; jj++) {
+      const int i = w + ii * nw, j = l + jj * 32;
+      if (i < d && j < dv) st[(size_t)i * dv + j] = S[ii][jj];
+    }
+}
+
 cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
                                    float *o, int H, int d, int dv, cudaStream_t st) {
   const int threads = 256;
+  if (d <= 128 && dv <= 128) {
+    const size_t sh = ((size_t)kLightChunk * (2 * d + dv) + (size_t)kLightChunk * 8 * dv) * sizeof(float);
+    static DeviceOnce once;
+    DIS_CUDA_TRY(once.run([&] {
+      cudaError_t e = cudaFuncSetAttribute(stack_lightning_reg_kernel<16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_lightning_reg_kernel<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    }));
+    if (d <= 64 && dv <= 64) stack_lightning_reg_kernel<8, 2><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
+    else stack_lightning_reg_kernel<16, 4><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
+    return cudaGetLastError();
+  }
   const size_t sh = ((size_t)d * dv + 2 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
   static DeviceOnce once;
@@ -104,19 +189,28 @@ cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, 
 // ------------------------------------------------------------------------------------------------ minimal gated recurrence
 // One thread per channel walks the span: z = sigmoid(pz), c = pu + 1/2 (pu >= 0) or sigmoid(pu), S = (1 - z) S + z c.
 template <bool F32>
-__global__ void stack_mingru_kernel(const float *proj, long long ld, float *state, StackSpans sp, void *out, int n) {
+__global__ void stack_mingru_kernel(const float *__restrict__ proj, long long ld, float *state, StackSpans sp, void *__restrict__ out, int n) {
   const int s = blockIdx.x;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
   float S = pos0 > 0 ? state[(long long)slot * n + i] : 0.f;
-  for (int t = 0; t < len; t++) {
-    const float *row = proj + (long long)(tok0 + t) * ld;
-    const float z = sigmoid_precise(row[i]);
-    const float u = row[n + i];
-    const float c = u >= 0.f ? u + 0.5f : sigmoid_precise(u);
-    S = (1.f - z) * S + z * c;
-    st_el<F32>(out, (long long)(tok0 + t) * n + i, S * silu_(row[2 * (long long)n + i]));
+  constexpr int U = 8;  // the gates read only the current token: eight tokens' inputs are fetched before the chain runs over them
+  for (int t0 = 0; t0 < len; t0 += U) {
+    float pz[U], pu[U], pg[U];
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+      const float *row = proj + (long long)(tok0 + min(t0 + k, len - 1)) * ld;
+      pz[k] = row[i]; pu[k] = row[n + i]; pg[k] = row[2 * (long long)n + i];
+    }
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+      if (t0 + k >= len) break;
+      const float z = sigmoid_precise(pz[k]);
+      const float c = pu[k] >= 0.f ? pu[k] + 0.5f : sigmoid_precise(pu[k]);
+      S = (1.f - z) * S + z * c;
+      st_el<F32>(out, (long long)(tok0 + t0 + k) * n + i, S * silu_(pg[k]));
+    }
   }
   state[(long long)slot * n + i] = S;
 }
