@@ -70,8 +70,103 @@ __global__ void __launch_bounds__(256) stack_gemm_kernel(StackGemm g) {
   }
 }
 
+// Few rows (decode passes, experts with a handful of tokens): the product is bound by reading W once.  A CTA takes one row tile
+// and 32 output columns; eight rows of A at a time sit in shared memory as fp32 (K in chunks of kFewK), a warp owns four
+// columns and its lanes stride over K eight elements at a time (16-byte loads of bf16 W), so each W element is read once per
+// eight rows; the lanes' partial sums are added across the warp at the end.
+constexpr int kFewK = 1024, kFewRows = 8, kFewCols = 32;
+template <bool WF32>
+__device__ __forceinline__ void ld_w8(const void *W, long long i, float (&w)[8]) {
+  if (WF32) {
+    const float4 a = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(W) + i);
+    const float4 b = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(W) + i + 4);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  } else {
+    const uint4 v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(W) + i);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) { w[2 * j] = __uint_as_float(u[j] << 16); w[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+  }
+}
+template <bool AF32, bool WF32>
+__global__ void __launch_bounds__(256) stack_gemm_few_kernel(StackGemm g) {
+  __shared__ __align__(16) float as[kFewRows][kFewK];
+  int row0, rows, grp = 0;
+  if (g.tiles) {
+    if ((int)blockIdx.x >= g.tiles[0]) return;
+    grp = g.tiles[1 + 3 * blockIdx.x];
+    row0 = g.tiles[2 + 3 * blockIdx.x];
+    rows = g.tiles[3 + 3 * blockIdx.x];
+  } else {
+    row0 = blockIdx.x * kStackGemmTile;
+    rows = min(kStackGemmTile, g.M - row0);
+  }
+  const int z = blockIdx.z;
+  const long long a_off = (long long)z * g.a_bs, w_off = (long long)z * g.w_bs + (long long)grp * (g.tiles ? g.w_bs : 0);
+  const float *bias = g.bias ? g.bias + (long long)z * g.bias_bs + (g.tiles ? (long long)grp * g.bias_bs : 0) : nullptr;
+  float *out = g.out + (long long)z * g.o_bs;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const int n0 = blockIdx.y * kFewCols + w * 4;
+  for (int r0 = 0; r0 < rows; r0 += kFewRows) {
+    const int nr = min(kFewRows, rows - r0);
+    float acc[4][kFewRows] = {};
+    for (int k0 = 0; k0 < g.K; k0 += kFewK) {
+      const int kc = min(kFewK, g.K - k0);
+      __syncthreads();
+      for (int rr = 0; rr < nr; rr++) {
+        const long long a_row = g.a_gather ? g.a_gather[row0 + r0 + rr] : row0 + r0 + rr;
+        for (int kk = threadIdx.x; kk < kc; kk += blockDim.x) as[rr][kk] = ld_el<AF32>(g.A, a_off + a_row * g.lda + k0 + kk);
+      }
+      __syncthreads();
+      for (int kk = l * 8; kk < kc; kk += 256) {
+        float wv[4][8];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          if (n0 + c < g.N) ld_w8<WF32>(g.W, w_off + (long long)(n0 + c) * g.ldw + k0 + kk, wv[c]);
+          else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) wv[c][j] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kFewRows; r++) {
+          if (r < nr) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&as[r][kk]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&as[r][kk + 4]);
+            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+              for (int j = 0; j < 8; j++) acc[c][r] = fmaf(av[j], wv[c][j], acc[c][r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+      for (int r = 0; r < kFewRows; r++) {
+        const float v = warp_sum(acc[c][r]);
+        if (l == 0 && r < nr && n0 + c < g.N) out[(long long)(row0 + r0 + r) * g.ldo + n0 + c] = v + (bias ? bias[n0 + c] : 0.f);
+      }
+  }
+}
+
 cudaError_t launch_stack_gemm(const StackGemm &g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return cudaSuccess;
+  // at most 64 rows in all and W rows that 16-byte loads can walk: the few-rows kernel
+  const long long wal = g.w_f32 ? 4 : 8;
+  const bool few = g.M <= 64 && g.K % 8 == 0 && g.ldw % wal == 0 && g.w_bs % wal == 0 &&
+                   reinterpret_cast<uintptr_t>(g.W) % 16 == 0;
+  if (few) {
+    dim3 grid(g.tiles ? g.max_tiles : (g.M + kStackGemmTile - 1) / kStackGemmTile, (g.N + kFewCols - 1) / kFewCols, g.batch);
+    if (grid.x == 0) return cudaSuccess;
+    if (g.a_f32 && g.w_f32) stack_gemm_few_kernel<true, true><<<grid, 256, 0, st>>>(g);
+    else if (g.a_f32) stack_gemm_few_kernel<true, false><<<grid, 256, 0, st>>>(g);
+    else if (g.w_f32) stack_gemm_few_kernel<false, true><<<grid, 256, 0, st>>>(g);
+    else stack_gemm_few_kernel<false, false><<<grid, 256, 0, st>>>(g);
+    return cudaGetLastError();
+  }
   dim3 grid(g.tiles ? g.max_tiles : (g.M + GB - 1) / GB, (g.N + GB - 1) / GB, g.batch);
   if (grid.x == 0) return cudaSuccess;
   if (g.a_f32 && g.w_f32) stack_gemm_kernel<true, true><<<grid, 256, 0, st>>>(g);
@@ -241,22 +336,25 @@ cudaError_t launch_stack_glu(const float *gu, void *act, bool f32, const int *ro
 }
 
 // ------------------------------------------------------------------------------------------------ router and expert rows
-// One warp per token: fp32 logits against the fp32 router matrix, then `top` rounds of arg-max (lowest index wins a tie), then
-// the softmax over the chosen logits.  E <= 1024 (logits sit in shared memory).
+// One block of four warps per token: the warps share the experts' fp32 logits against the fp32 router matrix (a warp per expert
+// at a time), then the first warp runs `top` rounds of arg-max (lowest index wins a tie) and the softmax over the chosen
+// logits.  E <= 1024 (logits sit in shared memory).
 template <bool F32>
-__global__ void stack_route_kernel(const void *hc, const float *router, int T, int W, int E, int top, int *idx, float *wt) {
-  extern __shared__ float zs[];  // [warps][E]
+__global__ void __launch_bounds__(128) stack_route_kernel(const void *hc, const float *__restrict__ router, int T, int W, int E, int top,
+                                                          int *idx, float *wt) {
+  extern __shared__ float zs[];  // [E]
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + w;
-  if (t >= T) return;
-  float *z = zs + (long long)w * E;
-  for (int e = 0; e < E; e++) {
+  const int t = blockIdx.x;
+  float *z = zs;
+  for (int e = w; e < E; e += 4) {
     float s = 0.f;
+#pragma unroll 4
     for (int i = l; i < W; i += 32) s = fmaf(ld_el<F32>(hc, (long long)t * W + i), router[(long long)e * W + i], s);
     s = warp_sum(s);
     if (l == 0) z[e] = s;
   }
-  __syncwarp();
+  __syncthreads();
+  if (w != 0) return;
   float m0 = 0.f, den = 0.f, mine = 0.f;
   for (int k = 0; k < top; k++) {
     float best = -INFINITY;
@@ -282,11 +380,10 @@ __global__ void stack_route_kernel(const void *hc, const float *router, int T, i
 cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
                                cudaStream_t st) {
   if (E > 1024 || top > 32 || top > E) return cudaErrorInvalidValue;
-  const int warps = 4;
-  const size_t sh = (size_t)warps * E * sizeof(float);
-  const int grid = (T + warps - 1) / warps;
-  if (f32) stack_route_kernel<true><<<grid, warps * 32, sh, st>>>(hc, router, T, W, E, top, idx, wt);
-  else stack_route_kernel<false><<<grid, warps * 32, sh, st>>>(hc, router, T, W, E, top, idx, wt);
+  if (T <= 0) return cudaSuccess;
+  const size_t sh = (size_t)E * sizeof(float);
+  if (f32) stack_route_kernel<true><<<T, 128, sh, st>>>(hc, router, T, W, E, top, idx, wt);
+  else stack_route_kernel<false><<<T, 128, sh, st>>>(hc, router, T, W, E, top, idx, wt);
   return cudaGetLastError();
 }
 

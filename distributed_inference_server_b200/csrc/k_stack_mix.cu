@@ -55,22 +55,40 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
   for (int i = threadIdx.x; i < d * dv; i += blockDim.x) st[i] = S[i];
 }
 
-// The same recurrence with the state in registers: thread (warp w, lane l) owns S[w + 8 ii][l + 32 jj], ii < RI, jj < RJ, for the
-// whole span; q, k, v of eight tokens at a time are staged in shared memory (SiLU applied), so the span costs two barriers per
-// eight tokens and no shared-memory traffic for the state.  Sums run in the order of the kernel above.
-constexpr int kLightChunk = 8;
-template <int RI, int RJ>
-__global__ void __launch_bounds__(256) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, const float *decay,
-                                                                  float *state, StackSpans sp, float *__restrict__ o, int H, int d, int dv) {
-  extern __shared__ float shm[];
-  const int s = blockIdx.x, h = blockIdx.y;
+// The same recurrence with the state in registers: thread (warp w, lane l) owns S[w RI + ii][l + 32 jj], ii < RI, jj < RJ; q, k, v
+// of eight tokens at a time are staged in shared memory (SiLU applied) while the next eight are already on their way in
+// registers, so a group costs two barriers and no shared-memory traffic for the state.
+// MODE 0: a whole span, from the slot's state (zero at position 0) back into it.
+// Long spans are cut into segments of kLightSeg tokens that run side by side (grid x = span * max_seg + segment):
+// MODE 1: the segment's own contribution sum_s a^(n-1-s) k_s v_s^T to the state at its end (no outputs), into `seg`;
+// a carry kernel then walks the segments in order, S_in(c+1) = a^n S_in(c) + contribution(c), leaving S_in(c) in `seg`;
+// MODE 2: the segment's outputs, starting from S_in(c).
+constexpr int kLightTok = 8, kLightSeg = 64;
+template <int RI, int RJ, int MODE>
+__global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, const float *decay,
+                                                                     float *state, StackSpans sp, float *__restrict__ o, int H, int d,
+                                                                     int dv, float *seg, int max_seg) {
+  extern __shared__ __align__(16) float shm[];
+  constexpr int DP = RI * 8, DVP = RJ * 32, LD = kLightTok * (2 * DP + DVP) / 256;
+  // heads vary fastest over the grid: the CTAs that run at the same time then read whole rows of the projections rather than
+  // one head's columns at a stride of a row, which would keep most memory channels idle
+  const int h = blockIdx.x % H, sc = blockIdx.x / H;
+  const int s = MODE == 0 ? sc : sc / max_seg;
   const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
-  constexpr int nw = 8;
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  float *qs = shm;                              // [chunk][d]
-  float *ks = qs + (size_t)kLightChunk * d;     // [chunk][d]
-  float *vs = ks + (size_t)kLightChunk * d;     // [chunk][dv]
-  float *part = vs + (size_t)kLightChunk * dv;  // [chunk][nw][dv]
+  int first = tok0, n = len;
+  float *sg = nullptr;
+  if (MODE != 0) {
+    const int c = sc - s * max_seg;
+    if (c * kLightSeg >= len) return;
+    first = tok0 + c * kLightSeg;
+    n = min(kLightSeg, len - c * kLightSeg);
+    sg = seg + ((size_t)(tok0 / kLightSeg + s + c) * H + h) * d * dv;
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, i0 = w * RI;
+  float *qs = shm;                             // [tok][DP]
+  float *ks = qs + kLightTok * DP;             // [tok][DP]
+  float *vs = ks + kLightTok * DP;             // [tok][DVP]
+  float *part = vs + kLightTok * DVP;          // [tok][8][DVP]
   float *st = state + ((long long)slot * H + h) * d * dv;
   const float a = decay[h];
   float S[RI][RJ];
@@ -78,71 +96,149 @@ __global__ void __launch_bounds__(256) stack_lightning_reg_kernel(const float *_
   for (int ii = 0; ii < RI; ii++)
 #pragma unroll
     for (int jj = 0; jj < RJ; jj++) {
-      const int i = w + ii * nw, j = l + jj * 32;
-      S[ii][jj] = (pos0 > 0 && i < d && j < dv) ? st[(size_t)i * dv + j] : 0.f;
+      const int i = i0 + ii, j = l + jj * 32;
+      float v = 0.f;
+      if (i < d && j < dv) {
+        if (MODE == 0 && pos0 > 0) v = st[(size_t)i * dv + j];
+        if (MODE == 2) v = sg[(size_t)i * dv + j];
+      }
+      S[ii][jj] = v;
     }
   const int per = 2 * d + dv;
-  for (int t0 = 0; t0 < len; t0 += kLightChunk) {
-    const int ct = min(kLightChunk, len - t0);
-    for (int e = threadIdx.x; e < ct * per; e += blockDim.x) {
-      const int t = e / per, c = e - t * per;
-      const float *row = proj + (long long)(tok0 + t0 + t) * ld;
-      if (c < d) qs[t * d + c] = silu_(row[(long long)h * d + c]);
-      else if (c < 2 * d) ks[t * d + c - d] = silu_(row[(long long)H * d + (long long)h * d + c - d]);
-      else vs[t * dv + c - 2 * d] = silu_(row[(long long)2 * H * d + (long long)h * dv + c - 2 * d]);
+  float tmp[LD];
+  auto fetch = [&](int t0) {
+    const int ct = min(kLightTok, n - t0);
+#pragma unroll
+    for (int u = 0; u < LD; u++) {
+      const int e = threadIdx.x + u * 256, t = e / per, c = e - t * per;
+      if (t < ct) {
+        const float *row = proj + (long long)(first + t0 + t) * ld;
+        const long long col = c < d ? (long long)h * d + c : c < 2 * d ? (long long)H * d + (long long)h * d + (c - d)
+                                                                        : (long long)2 * H * d + (long long)h * dv + (c - 2 * d);
+        tmp[u] = row[col];
+      }
     }
+  };
+  fetch(0);
+  for (int t0 = 0; t0 < n; t0 += kLightTok) {
+    const int ct = min(kLightTok, n - t0);
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < LD; u++) {
+      const int e = threadIdx.x + u * 256, t = e / per, c = e - t * per;
+      if (t < ct) {
+        float *dst = c < d ? qs + t * DP + c : c < 2 * d ? ks + t * DP + (c - d) : vs + t * DVP + (c - 2 * d);
+        *dst = silu_(tmp[u]);
+      }
+    }
+    if (t0 + kLightTok < n) fetch(t0 + kLightTok);
     __syncthreads();
     for (int t = 0; t < ct; t++) {
       float vj[RJ], acc[RJ];
 #pragma unroll
-      for (int jj = 0; jj < RJ; jj++) { vj[jj] = l + jj * 32 < dv ? vs[t * dv + l + jj * 32] : 0.f; acc[jj] = 0.f; }
+      for (int jj = 0; jj < RJ; jj++) { vj[jj] = l + jj * 32 < dv ? vs[t * DVP + l + jj * 32] : 0.f; acc[jj] = 0.f; }
 #pragma unroll
-      for (int ii = 0; ii < RI; ii++) {
-        const int i = w + ii * nw;
-        if (i < d) {
-          const float ki = ks[t * d + i], qi = qs[t * d + i];
+      for (int i4 = 0; i4 < RI; i4 += 4) {
+        const float4 k4 = *reinterpret_cast<const float4 *>(ks + t * DP + i0 + i4);
+        const float4 q4 = *reinterpret_cast<const float4 *>(qs + t * DP + i0 + i4);
+        const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-          for (int jj = 0; jj < RJ; jj++) {
-            S[ii][jj] = fmaf(a, S[ii][jj], ki * vj[jj]);
-            acc[jj] = fmaf(S[ii][jj], qi, acc[jj]);
+        for (int u = 0; u < 4; u++) {
+          if (i0 + i4 + u < d) {
+#pragma unroll
+            for (int jj = 0; jj < RJ; jj++) {
+              S[i4 + u][jj] = fmaf(a, S[i4 + u][jj], kv[u] * vj[jj]);
+              if (MODE != 1) acc[jj] = fmaf(S[i4 + u][jj], qv[u], acc[jj]);
+            }
           }
         }
       }
+      if (MODE != 1) {
 #pragma unroll
-      for (int jj = 0; jj < RJ; jj++)
-        if (l + jj * 32 < dv) part[((size_t)t * nw + w) * dv + l + jj * 32] = acc[jj];
+        for (int jj = 0; jj < RJ; jj++) part[(t * 8 + w) * DVP + l + jj * 32] = acc[jj];
+      }
     }
-    __syncthreads();
-    for (int e = threadIdx.x; e < ct * dv; e += blockDim.x) {
-      const int t = e / dv, j = e - t * dv;
-      float acc = 0.f;
-      for (int k = 0; k < nw; k++) acc += part[((size_t)t * nw + k) * dv + j];
-      o[(long long)(tok0 + t0 + t) * H * dv + (long long)h * dv + j] = acc;
+    if (MODE != 1) {
+      __syncthreads();
+      for (int e = threadIdx.x; e < ct * dv; e += blockDim.x) {
+        const int t = e / dv, j = e - t * dv;
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc += part[(t * 8 + k) * DVP + j];
+        o[(long long)(first + t0 + t) * H * dv + (long long)h * dv + j] = acc;
+      }
     }
   }
+  if (MODE == 2) return;
+  float *dst = MODE == 0 ? st : sg;
 #pragma unroll
   for (int ii = 0; ii < RI; ii++)
 #pragma unroll
     for (int jj = 0; jj < RJ; jj++) {
-      const int i = w + ii * nw, j = l + jj * 32;
-      if (i < d && j < dv) st[(size_t)i * dv + j] = S[ii][jj];
+      const int i = i0 + ii, j = l + jj * 32;
+      if (i < d && j < dv) dst[(size_t)i * dv + j] = S[ii][jj];
     }
 }
 
-cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
-                                   float *o, int H, int d, int dv, cudaStream_t st) {
-  const int threads = 256;
-  if (d <= 128 && dv <= 128) {
-    const size_t sh = ((size_t)kLightChunk * (2 * d + dv) + (size_t)kLightChunk * 8 * dv) * sizeof(float);
-    static DeviceOnce once;
-    DIS_CUDA_TRY(once.run([&] {
-      cudaError_t e = cudaFuncSetAttribute(stack_lightning_reg_kernel<16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-      return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_lightning_reg_kernel<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    }));
-    if (d <= 64 && dv <= 64) stack_lightning_reg_kernel<8, 2><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
-    else stack_lightning_reg_kernel<16, 4><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
+// Segment carry: one thread per state element walks the span's segments in order.  Elements vary fastest over the grid, then
+// heads, so that the CTAs that run at the same time walk one contiguous stretch of every segment.
+__global__ void stack_lightning_carry_kernel(const float *decay, float *state, StackSpans sp, float *seg, int H, int n_el) {
+  const int nz = (n_el + blockDim.x - 1) / blockDim.x;
+  const int z = blockIdx.x % nz, h = (blockIdx.x / nz) % H, s = blockIdx.x / (nz * H);
+  const int e = z * blockDim.x + threadIdx.x;
+  if (e >= n_el) return;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  float *st = state + ((long long)slot * H + h) * n_el;
+  const float a = decay[h];
+  float S = pos0 > 0 ? st[e] : 0.f;
+  float a64 = 1.f;
+  for (int k = 0; k < kLightSeg; k++) a64 *= a;
+  for (int c = 0; c * kLightSeg < len; c++) {
+    const int n = min(kLightSeg, len - c * kLightSeg);
+    float an = a64;
+    if (n < kLightSeg) {
+      an = 1.f;
+      for (int k = 0; k < n; k++) an *= a;
+    }
+    float *sg = seg + ((size_t)(tok0 / kLightSeg + s + c) * H + h) * n_el;
+    const float own = sg[e];
+    sg[e] = S;
+    S = fmaf(an, S, own);
+  }
+  st[e] = S;
+}
+
+int stack_lightning_seg_tokens() { return kLightSeg; }
+size_t stack_lightning_seg_floats(int cap_tokens, int max_spans, int H, int d, int dv) {
+  return (size_t)(cap_tokens / kLightSeg + max_spans + 1) * H * d * dv;
+}
+
+template <int RI, int RJ>
+static cudaError_t lightning_reg(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp, float *o,
+                                 int H, int d, int dv, float *seg, int max_len, cudaStream_t st) {
+  const size_t sh = (size_t)kLightTok * (2 * RI * 8 + RJ * 32 + 8 * RJ * 32) * sizeof(float);
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+  }));
+  if (!seg || max_len <= kLightSeg) {
+    stack_lightning_reg_kernel<RI, RJ, 0><<<sp.n_spans * H, 256, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv, nullptr, 1);
     return cudaGetLastError();
   }
+  const int max_seg = (max_len + kLightSeg - 1) / kLightSeg;
+  stack_lightning_reg_kernel<RI, RJ, 1><<<sp.n_spans * max_seg * H, 256, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_seg);
+  stack_lightning_carry_kernel<<<sp.n_spans * H * ((d * dv + 255) / 256), 256, 0, st>>>(decay, state, sp, seg, H, d * dv);
+  stack_lightning_reg_kernel<RI, RJ, 2><<<sp.n_spans * max_seg * H, 256, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_seg);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
+                                   float *o, int H, int d, int dv, float *seg, int max_len, cudaStream_t st) {
+  const int threads = 256;
+  if (d <= 64 && dv <= 64) return lightning_reg<8, 2>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_len, st);
+  if (d <= 128 && dv <= 128) return lightning_reg<16, 4>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_len, st);
   const size_t sh = ((size_t)d * dv + 2 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
   static DeviceOnce once;

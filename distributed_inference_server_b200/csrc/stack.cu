@@ -345,6 +345,15 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_p), M.lat_s_elems * 2));
     }
   }
+  {
+    // lightning: entry states of the segments of long spans (all layers share the buffer)
+    size_t seg = 0;
+    for (auto &L : M.layers)
+      if (L.c.mixer == DIS_MIX_LIGHTNING && L.c.dim <= 128 && L.c.vdim <= 128)
+        seg = std::max(seg, stack_lightning_seg_floats(cap_tokens, max_batch, L.c.heads, L.c.dim, L.c.vdim));
+    if (const char *g = getenv("DIS_STACK_LIGHT_SEGMENTS")) seg = atoi(g) != 0 ? seg : 0;
+    if (seg) ENG_CUDA(alloc(reinterpret_cast<void **>(&M.light_seg), seg * 4));
+  }
   if (stack_lat_rec) {
     M.lat_part_elems = (size_t)2048 * stack_lat_rec;  // (tokens x slices) of one pass
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_part), M.lat_part_elems * 4));
@@ -712,7 +721,12 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     int n_mix = 0;
     if (lc.mixer == DIS_MIX_LIGHTNING) {
       const int H = lc.heads, d = lc.dim, dv = lc.vdim;
-      RET_CUDA(launch_stack_lightning(M.proj, N, reinterpret_cast<const float *>(L.decay_d.ptr), L.state, sp, M.mix, H, d, dv, stream));
+      int max_len = 0;
+      for (auto &sh : stack_spans_h) max_len = std::max(max_len, sh.len);
+      const bool segments = M.light_seg && max_len > stack_lightning_seg_tokens() && d <= 128 && dv <= 128;
+      RET_CUDA(launch_stack_lightning(M.proj, N, reinterpret_cast<const float *>(L.decay_d.ptr), L.state, sp, M.mix, H, d, dv,
+                                      segments ? M.light_seg : nullptr, max_len, stream));
+      if (segments) kl += 2;
       RET_CUDA(launch_stack_norm_gate(M.mix, reinterpret_cast<const float *>(L.norm_w.ptr), M.proj + L.g_off, N, M.act, f32, T, H * dv, eps, stream));
       kl += 2;
       n_mix = H * dv;

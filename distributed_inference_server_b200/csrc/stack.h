@@ -53,8 +53,12 @@ cudaError_t launch_stack_canon(const float *hn, const float *w, float *state, co
                                int taps, cudaStream_t st);
 cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st);
 // proj [T][ld]: q at 0, k at H*d, v at 2*H*d (pre-activation).  state [slots][H][d][dv].  o [T][H*dv] fp32.
+// seg (or null): room for stack_lightning_seg_floats() floats -- spans longer than stack_lightning_seg_tokens() (max_len: the
+// longest span of the pass) are then cut into segments that run side by side, with a carry pass between them.
+size_t stack_lightning_seg_floats(int cap_tokens, int max_spans, int H, int d, int dv);
+int stack_lightning_seg_tokens();
 cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
-                                   float *o, int H, int d, int dv, cudaStream_t st);
+                                   float *o, int H, int d, int dv, float *seg, int max_len, cudaStream_t st);
 // out = unit_rms(o) * w * sigmoid(gate) per token over n = H*dv coordinates; gate [T][ldg]
 cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *gate, long long ldg, void *out, bool f32, int T,
                                    int n, float eps, cudaStream_t st);
@@ -156,6 +160,7 @@ struct StackModel {
   size_t lat_s_elems = 0;
   uint16_t *lat_qb = nullptr, *lat_cg = nullptr, *lat_cgt = nullptr, *lat_p = nullptr;
   float *lat_s = nullptr;
+  float *light_seg = nullptr; // lightning: entry states of the segments of long spans
   float *lat_part = nullptr;  // latent attention: slice records
   size_t lat_part_elems = 0;
   float *scratch = nullptr;  // split-K slices of the tensor-core products

@@ -10,7 +10,7 @@ from tests import _stack_util as U
 
 pytestmark = pytest.mark.gpu
 F32_TOL = 2e-4   # float32 engine against the float64 oracle (these narrow random models are not well conditioned everywhere)
-SAME = 2e-6      # two float32 schedules of the same tokens against each other
+SAME = 4e-6      # two float32 schedules of the same tokens against each other
 
 
 def toks(n, vocab=50, seed=0):
@@ -96,6 +96,50 @@ def test_portions_of_several_sizes(sizes):
     e.close()
     assert U.rel_err(got, want) < F32_TOL
     assert U.rel_err(got, U.run_whole(cfg, W, t)) < SAME
+
+
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 16), (1, 72, 40), (3, 128, 128)])
+def test_long_recurrent_spans_run_as_segments_with_a_carry(heads, dim, vdim):
+    """A span longer than a segment (64 tokens) of the decayed linear-attention scan, or of the gated recurrence, is cut into
+    segments that run side by side and are joined by a carry pass.  Spans of one token, of exactly one or two segments, with a
+    ragged last segment and with a start in the middle of a sequence share passes here; all must agree with the oracle and
+    with token-by-token feeding."""
+    cfg = U.config([(U.lightning(heads=heads, dim=dim, vdim=vdim, decay=[0.999, 0.93, 0.5][:heads]), None), (U.mingru(24), None)],
+                   width=40)
+    W = U.weights(cfg, seed=61)
+    a, b, c = toks(300, seed=41), toks(140, seed=42), toks(129, seed=43)
+    wa, wb, wc = (U.oracle_logits(cfg, W, t) for t in (a, b, c))
+    e = U.engine(cfg, W, pool_tokens=640, page_size=16)
+    f = U.Feeder(e)
+    f.step([("a", a, 130), ("b", b, 1), ("c", c, 64)])
+    f.step([("a", a, 1), ("b", b, 128), ("c", c, 65)])
+    f.step([("a", a, 169), ("b", b, 11)])
+    ga, gb, gc = f.end("a"), f.end("b"), f.end("c")
+    for _ in c:
+        f.step([("s", c, 1)])
+    gs = f.end("s")
+    e.close()
+    assert max(U.rel_err(ga, wa), U.rel_err(gb, wb), U.rel_err(gc, wc)) < F32_TOL
+    assert U.rel_err(gs, gc) < 1e-5
+
+
+def test_few_rows_product_agrees_with_the_tiled_one():
+    """Passes of at most 64 rows take the product kernel that streams the weights once (experts with a few tokens, decode);
+    larger passes the tiled one.  The same tokens fed both ways must give the same logits."""
+    cfg = U.config([(U.latent(heads=2, dim=8, rot_dim=8, vdim=16, kv_rank=24), U.moe(ff=16, experts=4, top=2)),
+                    (U.mingru(32), U.dense(ff=40))], width=32)
+    W = U.weights(cfg, seed=67)
+    t = toks(100, seed=44)
+    want = U.oracle_logits(cfg, W, t)
+    whole = U.run_whole(cfg, W, t)
+    e = U.engine(cfg, W)
+    f = U.Feeder(e)
+    for n in [30, 9, 1, 1, 40, 19]:
+        f.step([("a", t, n)])
+    got = f.end("a")
+    e.close()
+    assert U.rel_err(whole, want) < F32_TOL and U.rel_err(got, want) < F32_TOL
+    assert U.rel_err(got, whole) < 1e-5
 
 
 def test_long_portions_in_bfloat16_take_the_matrix_product_path():
