@@ -317,21 +317,24 @@ cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long
 
 // ------------------------------------------------------------------------------------------------ clamped gated unit
 template <bool F32>
-__global__ void stack_glu_kernel(const float *gu, void *act, const int *rows_ptr, int M, int ff, float limit) {
-  const long long rows = rows_ptr ? min(M, rows_ptr[0]) : M;
-  const long long n = rows * ff;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / ff, c = i % ff;
-    const float g = fminf(gu[r * 2 * ff + c], limit);
-    const float u = fminf(fmaxf(gu[r * 2 * ff + ff + c], -limit), limit);
-    st_el<F32>(act, i, g * sigmoid_precise(1.702f * g) * (u + 1.f));
+__global__ void stack_glu_kernel(const float *__restrict__ gu, const float *__restrict__ bias, void *__restrict__ act, const int *rows_ptr,
+                                 int M, int ff, float limit) {
+  const int rows = rows_ptr ? min(M, rows_ptr[0]) : M;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float *gr = gu + (long long)r * 2 * ff;
+    for (int c = threadIdx.x; c < ff; c += blockDim.x) {
+      const float g = fminf(gr[c] + (bias ? bias[c] : 0.f), limit);
+      const float u = fminf(fmaxf(gr[ff + c] + (bias ? bias[ff + c] : 0.f), -limit), limit);
+      st_el<F32>(act, (long long)r * ff + c, g * sigmoid_precise(1.702f * g) * (u + 1.f));
+    }
   }
 }
-cudaError_t launch_stack_glu(const float *gu, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit, cudaStream_t st) {
+cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
+                             cudaStream_t st) {
   if (M <= 0) return cudaSuccess;
-  const int grid = (int)std::min<long long>(((long long)M * ff + 255) / 256, 148 * 8);
-  if (f32) stack_glu_kernel<true><<<grid, 256, 0, st>>>(gu, act, rows_ptr, M, ff, limit);
-  else stack_glu_kernel<false><<<grid, 256, 0, st>>>(gu, act, rows_ptr, M, ff, limit);
+  const int grid = std::min(M, 148 * 16);
+  if (f32) stack_glu_kernel<true><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+  else stack_glu_kernel<false><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
   return cudaGetLastError();
 }
 

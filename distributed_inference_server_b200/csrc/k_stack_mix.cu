@@ -193,17 +193,28 @@ __global__ void stack_lightning_carry_kernel(const float *decay, float *state, S
   float S = pos0 > 0 ? st[e] : 0.f;
   float a64 = 1.f;
   for (int k = 0; k < kLightSeg; k++) a64 *= a;
-  for (int c = 0; c * kLightSeg < len; c++) {
-    const int n = min(kLightSeg, len - c * kLightSeg);
-    float an = a64;
-    if (n < kLightSeg) {
-      an = 1.f;
-      for (int k = 0; k < n; k++) an *= a;
+  const int nseg = (len + kLightSeg - 1) / kLightSeg;
+  float *sg0 = seg + ((size_t)(tok0 / kLightSeg + s) * H + h) * n_el + e;
+  const size_t step = (size_t)H * n_el;
+  constexpr int U = 8;  // segments whose contributions are fetched together, ahead of the chain that joins them
+  for (int c0 = 0; c0 < nseg; c0 += U) {
+    float own[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) own[u] = c0 + u < nseg ? sg0[(size_t)(c0 + u) * step] : 0.f;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int c = c0 + u;
+      if (c < nseg) {
+        const int n = min(kLightSeg, len - c * kLightSeg);
+        float an = a64;
+        if (n < kLightSeg) {
+          an = 1.f;
+          for (int k = 0; k < n; k++) an *= a;
+        }
+        sg0[(size_t)c * step] = S;
+        S = fmaf(an, S, own[u]);
+      }
     }
-    float *sg = seg + ((size_t)(tok0 / kLightSeg + s + c) * H + h) * n_el;
-    const float own = sg[e];
-    sg[e] = S;
-    S = fmaf(an, S, own);
   }
   st[e] = S;
 }
@@ -267,29 +278,64 @@ cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *
   return cudaGetLastError();
 }
 
+// heads > 0: o is laid out head by head, [heads][T][n / heads] (the per-head tensor-core products write it so)
 template <bool F32>
-__global__ void stack_gate_kernel(const float *o, const float *gate, long long ldg, void *out, int T, int n) {
-  const long long tot = (long long)T * n;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < tot; i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / n, c = i % n;
-    st_el<F32>(out, i, o[i] * sigmoid_precise(gate[t * ldg + c]));
+__global__ void stack_gate_kernel(const float *__restrict__ o, const float *__restrict__ gate, long long ldg, void *__restrict__ out, int T,
+                                  int n, int heads) {
+  const int hw = heads > 0 ? n / heads : n;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      const float v = heads > 0 ? o[((long long)(c / hw) * T + t) * hw + c % hw] : o[(long long)t * n + c];
+      st_el<F32>(out, (long long)t * n + c, v * sigmoid_precise(gate[t * ldg + c]));
+    }
   }
 }
-cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, void *out, bool f32, int T, int n, cudaStream_t st) {
-  const int grid = (int)std::min<long long>(((long long)T * n + 255) / 256, 148 * 8);
-  if (f32) stack_gate_kernel<true><<<grid, 256, 0, st>>>(o, gate, ldg, out, T, n);
-  else stack_gate_kernel<false><<<grid, 256, 0, st>>>(o, gate, ldg, out, T, n);
+cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, void *out, bool f32, int T, int n, int heads,
+                              cudaStream_t st) {
+  if (T <= 0) return cudaSuccess;
+  const int grid = std::min(T, 148 * 16);
+  if (f32) stack_gate_kernel<true><<<grid, 256, 0, st>>>(o, gate, ldg, out, T, n, heads);
+  else stack_gate_kernel<false><<<grid, 256, 0, st>>>(o, gate, ldg, out, T, n, heads);
+  return cudaGetLastError();
+}
+
+// Per-head products on the tensor cores want each head's rows contiguous: src fp32 [T][ld], head h at columns off + h * hs,
+// `wd` of them -> dst bf16 [H][T][wd]; and back: src fp32 [H][T][wd] -> dst fp32 [T][ld] at columns off + h * hs.
+__global__ void stack_heads_pack_kernel(const float *__restrict__ src, long long ld, int off, int hs, int wd, int T, int H,
+                                        uint16_t *__restrict__ dst) {
+  const int t = blockIdx.x / H, h = blockIdx.x - t * H;  // one (token, head) row per block
+  const float *sr = src + (long long)t * ld + off + (long long)h * hs;
+  uint16_t *dr = dst + ((long long)h * T + t) * wd;
+  for (int c = threadIdx.x; c < wd; c += blockDim.x) dr[c] = float_to_bf16_bits(sr[c]);
+}
+__global__ void stack_heads_unpack_kernel(const float *__restrict__ src, int wd, int T, int H, float *__restrict__ dst, long long ld,
+                                          int off, int hs) {
+  const int t = blockIdx.x / H, h = blockIdx.x - t * H;
+  const float *sr = src + ((long long)h * T + t) * wd;
+  float *dr = dst + (long long)t * ld + off + (long long)h * hs;
+  for (int c = threadIdx.x; c < wd; c += blockDim.x) dr[c] = sr[c];
+}
+cudaError_t launch_stack_heads_pack(const float *src, long long ld, int off, int hs, int wd, int T, int H, uint16_t *dst, cudaStream_t st) {
+  if ((long long)T * H <= 0 || wd <= 0) return cudaSuccess;
+  stack_heads_pack_kernel<<<T * H, 128, 0, st>>>(src, ld, off, hs, wd, T, H, dst);
+  return cudaGetLastError();
+}
+cudaError_t launch_stack_heads_unpack(const float *src, int wd, int T, int H, float *dst, long long ld, int off, int hs, cudaStream_t st) {
+  if ((long long)T * H <= 0 || wd <= 0) return cudaSuccess;
+  stack_heads_unpack_kernel<<<T * H, 128, 0, st>>>(src, wd, T, H, dst, ld, off, hs);
   return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------ minimal gated recurrence
 // One thread per channel walks the span: z = sigmoid(pz), c = pu + 1/2 (pu >= 0) or sigmoid(pu), S = (1 - z) S + z c.
 template <bool F32>
-__global__ void stack_mingru_kernel(const float *__restrict__ proj, long long ld, float *state, StackSpans sp, void *__restrict__ out, int n) {
+__global__ void stack_mingru_kernel(const float *__restrict__ proj, long long ld, const float *bias, float *state, StackSpans sp,
+                                    void *__restrict__ out, int n) {
   const int s = blockIdx.x;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  const float bz = bias ? bias[i] : 0.f, bu = bias ? bias[n + i] : 0.f, bg = bias ? bias[2 * (long long)n + i] : 0.f;
   float S = pos0 > 0 ? state[(long long)slot * n + i] : 0.f;
   constexpr int U = 8;  // the gates read only the current token: eight tokens' inputs are fetched before the chain runs over them
   for (int t0 = 0; t0 < len; t0 += U) {
@@ -297,7 +343,7 @@ __global__ void stack_mingru_kernel(const float *__restrict__ proj, long long ld
 #pragma unroll
     for (int k = 0; k < U; k++) {
       const float *row = proj + (long long)(tok0 + min(t0 + k, len - 1)) * ld;
-      pz[k] = row[i]; pu[k] = row[n + i]; pg[k] = row[2 * (long long)n + i];
+      pz[k] = row[i] + bz; pu[k] = row[n + i] + bu; pg[k] = row[2 * (long long)n + i] + bg;
     }
 #pragma unroll
     for (int k = 0; k < U; k++) {
@@ -310,11 +356,78 @@ __global__ void stack_mingru_kernel(const float *__restrict__ proj, long long ld
   }
   state[(long long)slot * n + i] = S;
 }
-cudaError_t launch_stack_mingru(const float *proj, long long ld, float *state, const StackSpans &sp, void *out, bool f32, int n,
-                                cudaStream_t st) {
+// Long spans: a block owns 32 channels (lanes) and cuts the span into kGruSlices time slices (warps).  The update is linear in the
+// state, S_t = (1 - z_t) S_(t-1) + z_t c_t, so a slice is summarised by the pair (A, B) with S_end = A S_begin + B; the warps
+// exchange the pairs through shared memory, each folds the pairs of the slices before its own onto the slot's state, and
+// then walks its slice a second time from that state, writing the outputs.
+constexpr int kGruSlices = 16;
+template <bool F32>
+__global__ void __launch_bounds__(kGruSlices * 32) stack_mingru_sliced_kernel(const float *__restrict__ proj, long long ld,
+                                                                              const float *bias, float *state, StackSpans sp,
+                                                                              void *__restrict__ out, int n, int n_cb) {
+  __shared__ float As[kGruSlices][32], Bs[kGruSlices][32];
+  const int s = blockIdx.x / n_cb, cb = blockIdx.x - s * n_cb;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const int i = cb * 32 + l;
+  const bool on = i < n;
+  const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
+  const int per = (len + kGruSlices - 1) / kGruSlices;
+  const int t_lo = min(len, w * per), t_hi = min(len, t_lo + per);
+  constexpr int U = 8;
+  const float bz = bias && on ? bias[i] : 0.f, bu = bias && on ? bias[n + i] : 0.f, bg = bias && on ? bias[2 * (long long)n + i] : 0.f;
+  float A = 1.f, B = 0.f;
+  for (int t0 = t_lo; t0 < t_hi && on; t0 += U) {
+    float pz[U], pu[U];
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+      const float *row = proj + (long long)(tok0 + min(t0 + k, t_hi - 1)) * ld;
+      pz[k] = row[i] + bz; pu[k] = row[n + i] + bu;
+    }
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+      if (t0 + k >= t_hi) break;
+      const float z = sigmoid_precise(pz[k]);
+      const float c = pu[k] >= 0.f ? pu[k] + 0.5f : sigmoid_precise(pu[k]);
+      A *= 1.f - z;
+      B = (1.f - z) * B + z * c;
+    }
+  }
+  As[w][l] = A; Bs[w][l] = B;
+  __syncthreads();
+  if (!on) return;
+  float S = pos0 > 0 ? state[(long long)slot * n + i] : 0.f;
+  for (int k = 0; k < w; k++) S = fmaf(As[k][l], S, Bs[k][l]);
+  for (int t0 = t_lo; t0 < t_hi; t0 += U) {
+    float pz[U], pu[U], pg[U];
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+      const float *row = proj + (long long)(tok0 + min(t0 + k, t_hi - 1)) * ld;
+      pz[k] = row[i] + bz; pu[k] = row[n + i] + bu; pg[k] = row[2 * (long long)n + i] + bg;
+    }
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+      if (t0 + k >= t_hi) break;
+      const float z = sigmoid_precise(pz[k]);
+      const float c = pu[k] >= 0.f ? pu[k] + 0.5f : sigmoid_precise(pu[k]);
+      S = (1.f - z) * S + z * c;
+      st_el<F32>(out, (long long)(tok0 + t0 + k) * n + i, S * silu_(pg[k]));
+    }
+  }
+  // the state after the span: the last slice that holds tokens ends at the span's end
+  if (t_hi == len && t_lo < len) state[(long long)slot * n + i] = S;
+}
+
+cudaError_t launch_stack_mingru(const float *proj, long long ld, const float *bias, float *state, const StackSpans &sp, void *out,
+                                bool f32, int n, int max_len, cudaStream_t st) {
+  if (max_len >= 4 * kGruSlices) {
+    const int n_cb = (n + 31) / 32;
+    if (f32) stack_mingru_sliced_kernel<true><<<sp.n_spans * n_cb, kGruSlices * 32, 0, st>>>(proj, ld, bias, state, sp, out, n, n_cb);
+    else stack_mingru_sliced_kernel<false><<<sp.n_spans * n_cb, kGruSlices * 32, 0, st>>>(proj, ld, bias, state, sp, out, n, n_cb);
+    return cudaGetLastError();
+  }
   dim3 grid(sp.n_spans, (n + 127) / 128);
-  if (f32) stack_mingru_kernel<true><<<grid, 128, 0, st>>>(proj, ld, state, sp, out, n);
-  else stack_mingru_kernel<false><<<grid, 128, 0, st>>>(proj, ld, state, sp, out, n);
+  if (f32) stack_mingru_kernel<true><<<grid, 128, 0, st>>>(proj, ld, bias, state, sp, out, n);
+  else stack_mingru_kernel<false><<<grid, 128, 0, st>>>(proj, ld, bias, state, sp, out, n);
   return cudaGetLastError();
 }
 

@@ -679,8 +679,11 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   // Dense projection out[Mrows][N] = A[Mrows][K] W[N][K]^T (+ bias).  bf16 operands go to the tcgen05 product the Llama path
   // uses (fp32 accumulation in TMEM; split-K slices summed, with the bias, by one more kernel); float operands, and shapes a
   // TMA map cannot describe (K not a multiple of 8), to the fp32-FMA product.  a_rows: rows the buffer behind A holds.
+  // later_bias: the caller's next kernel can add the bias itself; it is set to the bias when this product left it out (a
+  // single-slice tensor-core product, which has no pass of its own over the result) and to null when it is already in.
   auto gemm = [&](const void *A, bool a_f32, long long lda, const StackTensor &Wt, size_t w_off, const float *bias, float *out,
-                  int Mrows, int N, int K, int a_rows = 0) -> cudaError_t {
+                  int Mrows, int N, int K, int a_rows = 0, const float **later_bias = nullptr) -> cudaError_t {
+    if (later_bias) *later_bias = nullptr;
     if (stack_tc && !f32 && !a_f32 && !Wt.f32 && a_rows > 0 && K % 8 == 0 && lda == K && (w_off * 2) % 16 == 0) {
       const TmaMap *xm = stack_map(A, (uint64_t)a_rows, (uint64_t)K, (uint32_t)gemm_token_tile(Mrows));
       const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(Wt.ptr) + w_off, (uint64_t)N, (uint64_t)K, 128);
@@ -688,6 +691,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       int s = gemm_pick_split_k(Mrows, N, K);
       if ((size_t)s * Mrows * N > M.scratch_elems) s = 1;
       kl++;
+      if (s == 1 && bias && later_bias) { *later_bias = bias; bias = nullptr; }
       if (s == 1 && !bias) return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, stream);
       if ((size_t)s * Mrows * N > M.scratch_elems) return cudaErrorInvalidValue;
       RET_CUDA(launch_gemm_partial(*wm, *xm, M.scratch, Mrows, N, K, 0, s, stream));
@@ -717,7 +721,9 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     const dis_layer_config &lc = L.c;
     RET_CUDA(sublayer_in(L.g4 + 0, L.canon1, L.cstate1));
     const int N = L.n_in;
-    RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W, cap_tokens));
+    const float *in_bias = nullptr;  // minGRU adds its projections' biases itself when the product left them out
+    RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W, cap_tokens,
+                  lc.mixer == DIS_MIX_MINGRU ? &in_bias : nullptr));
     int n_mix = 0;
     if (lc.mixer == DIS_MIX_LIGHTNING) {
       const int H = lc.heads, d = lc.dim, dv = lc.vdim;
@@ -731,7 +737,9 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       kl += 2;
       n_mix = H * dv;
     } else if (lc.mixer == DIS_MIX_MINGRU) {
-      RET_CUDA(launch_stack_mingru(M.proj, N, L.state, sp, M.act, f32, lc.width, stream)); kl++;
+      int max_len = 0;
+      for (auto &sh : stack_spans_h) max_len = std::max(max_len, sh.len);
+      RET_CUDA(launch_stack_mingru(M.proj, N, in_bias, L.state, sp, M.act, f32, lc.width, max_len, stream)); kl++;
       n_mix = lc.width;
     } else {
       const int H = lc.heads, d = lc.dim, dr = lc.rot_dim, dv = lc.vdim, r = lc.kv_rank, D = r + dr;
@@ -739,13 +747,29 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       StackLayer &KV = M.layers[(size_t)L.kv_layer];
       RET_CUDA(launch_stack_latent_prep(M.proj, N, L.q_off, L.dkv_off, lc.kv_from < 0 ? reinterpret_cast<const float *>(L.norm_w.ptr) : nullptr, sl, sp,
                                         M.qf, lc.kv_from < 0 ? L.pool : nullptr, f32, d_page_table, max_pages, page_size, stream));
-      // absorbed queries: qf[t][h][0..r) = sum_a q[t][h][a] * uk[h*d + a][.]  (one batch entry per head)
-      StackGemm g;
-      g.A = M.proj + L.q_off; g.a_f32 = true; g.lda = N; g.a_bs = d + dr;
-      g.W = L.ukT.ptr; g.w_f32 = L.ukT.f32; g.ldw = d; g.w_bs = (long long)r * d;
-      g.out = M.qf; g.ldo = (long long)H * D; g.o_bs = D;
-      g.M = T; g.N = r; g.K = d; g.batch = H;
-      RET_CUDA(launch_stack_gemm(g, stream));
+      // absorbed queries: qf[t][h][0..r) = sum_a q[t][h][a] * uk[h*d + a][.]  (one batch entry per head).  Large bf16 passes:
+      // one tensor-core product per head over the head's queries packed contiguously; else the batched fp32-FMA product.
+      const bool head_tc = M.lat_gemm && T >= 256 && !L.ukT.f32 && !L.uv.f32 && d % 8 == 0 && ((size_t)r * d * 2) % 16 == 0 &&
+                           ((size_t)dv * r * 2) % 16 == 0 && ((size_t)T * d * 2) % 16 == 0 && ((size_t)T * r * 2) % 16 == 0;
+      if (head_tc) {
+        RET_CUDA(launch_stack_heads_pack(M.proj, N, L.q_off, d + dr, d, T, H, M.lat_qb, stream));
+        for (int h = 0; h < H; h++) {
+          TmaMap xm;
+          RET_CUDA(make_tma_map_2d(&xm, M.lat_qb + (size_t)h * T * d, (uint64_t)T, (uint64_t)d, (uint32_t)gemm_token_tile(T)));
+          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.ukT.ptr) + (size_t)h * r * d, (uint64_t)r, (uint64_t)d, 128);
+          if (!wm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_partial(*wm, xm, M.mix2 + (size_t)h * T * r, T, r, d, 0, 1, stream));
+        }
+        RET_CUDA(launch_stack_heads_unpack(M.mix2, r, T, H, M.qf, (long long)H * D, 0, D, stream));
+        kl += H + 1;
+      } else {
+        StackGemm g;
+        g.A = M.proj + L.q_off; g.a_f32 = true; g.lda = N; g.a_bs = d + dr;
+        g.W = L.ukT.ptr; g.w_f32 = L.ukT.f32; g.ldw = d; g.w_bs = (long long)r * d;
+        g.out = M.qf; g.ldo = (long long)H * D; g.o_bs = D;
+        g.M = T; g.N = r; g.K = d; g.batch = H;
+        RET_CUDA(launch_stack_gemm(g, stream));
+      }
       RET_CUDA(launch_stack_latent_attn(M.qf, KV.pool, f32, reinterpret_cast<const float *>(L.sink.ptr), sl, sp, mt.d<int>(mt.o_ab_tok0),
                                         mt.d<int>(mt.o_ab_len), n_qb, d_page_table, max_pages, page_size, M.mix, lat_split, lat_keys,
                                         M.lat_part, stream));
@@ -778,13 +802,26 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
         }
       }
       // values: mix2[t][h][0..dv) = sum_b ol[t][h][b] * uv[h*dv + .][b]
-      StackGemm v;
-      v.A = M.mix; v.a_f32 = true; v.lda = (long long)H * r; v.a_bs = r;
-      v.W = L.uv.ptr; v.w_f32 = L.uv.f32; v.ldw = r; v.w_bs = (long long)dv * r;
-      v.out = M.mix2; v.ldo = (long long)H * dv; v.o_bs = dv;
-      v.M = T; v.N = dv; v.K = r; v.batch = H;
-      RET_CUDA(launch_stack_gemm(v, stream));
-      RET_CUDA(launch_stack_gate(M.mix2, M.proj + L.g_off, N, M.act, f32, T, H * dv, stream));
+      if (head_tc) {
+        RET_CUDA(launch_stack_heads_pack(M.mix, (long long)H * r, 0, r, r, T, H, M.lat_qb, stream));
+        for (int h = 0; h < H; h++) {
+          TmaMap xm;
+          RET_CUDA(make_tma_map_2d(&xm, M.lat_qb + (size_t)h * T * r, (uint64_t)T, (uint64_t)r, (uint32_t)gemm_token_tile(T)));
+          const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(L.uv.ptr) + (size_t)h * dv * r, (uint64_t)dv, (uint64_t)r, 128);
+          if (!wm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_partial(*wm, xm, M.mix2 + (size_t)h * T * dv, T, dv, r, 0, 1, stream));
+        }
+        RET_CUDA(launch_stack_gate(M.mix2, M.proj + L.g_off, N, M.act, f32, T, H * dv, H, stream));
+        kl += H;
+      } else {
+        StackGemm v;
+        v.A = M.mix; v.a_f32 = true; v.lda = (long long)H * r; v.a_bs = r;
+        v.W = L.uv.ptr; v.w_f32 = L.uv.f32; v.ldw = r; v.w_bs = (long long)dv * r;
+        v.out = M.mix2; v.ldo = (long long)H * dv; v.o_bs = dv;
+        v.M = T; v.N = dv; v.K = r; v.batch = H;
+        RET_CUDA(launch_stack_gemm(v, stream));
+        RET_CUDA(launch_stack_gate(M.mix2, M.proj + L.g_off, N, M.act, f32, T, H * dv, 0, stream));
+      }
       kl += 5;
       n_mix = H * dv;
     }
@@ -794,8 +831,9 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     RET_CUDA(sublayer_in(L.g4 + 2, L.canon2, L.cstate2));
     if (lc.mlp == DIS_MLP_DENSE) {
       const int ff = lc.ff;
-      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens));
-      RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, T, ff, lc.limit, stream)); kl++;
+      const float *gu_bias = nullptr;
+      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias));
+      RET_CUDA(launch_stack_glu(M.proj, gu_bias, M.act, f32, nullptr, T, ff, lc.limit, stream)); kl++;
       RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
@@ -819,7 +857,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
           RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, stream));
           off += cnt; kl++;
         }
-        RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, rows, ff, lc.limit, stream));
+        RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, stream));
         off = 0;
         for (int e = 0; e < E; e++) {
           const int cnt = M.h_counts[e];
@@ -842,7 +880,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       g.out = M.proj; g.ldo = 2 * ff; g.M = rows; g.N = 2 * ff; g.K = W;
       g.tiles = M.tiles; g.max_tiles = tiles_cap;
       RET_CUDA(launch_stack_gemm(g, stream));
-      RET_CUDA(launch_stack_glu(M.proj, M.act, f32, nullptr, rows, ff, lc.limit, stream));
+      RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, stream));
       StackGemm dn;
       dn.A = M.act; dn.a_f32 = f32; dn.lda = ff;
       dn.W = L.w_down.ptr; dn.w_f32 = L.w_down.f32; dn.ldw = ff; dn.w_bs = (long long)W * ff;

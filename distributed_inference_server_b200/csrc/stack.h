@@ -62,11 +62,17 @@ cudaError_t launch_stack_lightning(const float *proj, long long ld, const float 
 // out = unit_rms(o) * w * sigmoid(gate) per token over n = H*dv coordinates; gate [T][ldg]
 cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *gate, long long ldg, void *out, bool f32, int T,
                                    int n, float eps, cudaStream_t st);
-// out = o * sigmoid(gate)
-cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, void *out, bool f32, int T, int n, cudaStream_t st);
+// out = o * sigmoid(gate); heads > 0: o is [heads][T][n / heads] instead of [T][n]
+cudaError_t launch_stack_gate(const float *o, const float *gate, long long ldg, void *out, bool f32, int T, int n, int heads,
+                              cudaStream_t st);
+// head h of src [T][ld] (columns off + h * hs .. + wd) -> dst bf16 [H][T][wd], and fp32 [H][T][wd] back into such columns
+cudaError_t launch_stack_heads_pack(const float *src, long long ld, int off, int hs, int wd, int T, int H, uint16_t *dst, cudaStream_t st);
+cudaError_t launch_stack_heads_unpack(const float *src, int wd, int T, int H, float *dst, long long ld, int off, int hs, cudaStream_t st);
 // proj [T][ld]: z at 0, u at n, g at 2n (biases already added).  state [slots][n].
-cudaError_t launch_stack_mingru(const float *proj, long long ld, float *state, const StackSpans &sp, void *out, bool f32, int n,
-                                cudaStream_t st);
+// max_len: the longest span of the pass (long spans are cut into time slices that run side by side)
+// bias (or null): [3n], added to proj here when the product that made proj left it out
+cudaError_t launch_stack_mingru(const float *proj, long long ld, const float *bias, float *state, const StackSpans &sp, void *out,
+                                bool f32, int n, int max_len, cudaStream_t st);
 // Latent attention, step 1: per token, the rotated query parts go to qf[T][H][r+dr] (+r), and -- when pool is given --
 // the normed latent and the rotated shared key part go to the token's row of the page pool ([pages*page_size][r+dr]).
 struct StackLatent {
@@ -92,7 +98,9 @@ cudaError_t launch_stack_latent_gather(const void *pool, const int *pt_row, int 
 cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const float *sink, int H, int pos_first, float scale,
                                         uint16_t *P, cudaStream_t st);
 // act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu [M][2*ff] (gate | up)
-cudaError_t launch_stack_glu(const float *gu, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit, cudaStream_t st);
+// bias (or null): [2*ff], added to gu here when the product that made gu left it out
+cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
+                             cudaStream_t st);
 // Router: logits in fp32 from hc and the fp32 router matrix; top-k by value (lowest index wins a tie); softmax over the chosen.
 cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
                                cudaStream_t st);

@@ -164,6 +164,28 @@ def test_long_portions_in_bfloat16_take_the_matrix_product_path():
     assert float(np.median(U.row_errs(ga, wa))) < 2e-2
 
 
+def test_passes_of_256_tokens_in_bfloat16_run_the_head_products_on_tensor_cores():
+    """From 256 tokens in a pass, the query absorption and the value expansion of latent attention run as one tensor-core
+    product per head over that head's rows packed together (bfloat16; dim, kv_rank and kv_rank + rot_dim multiples of 8).
+    A pass above and one below that size, two sequences in one pass, against the oracle and against each other."""
+    cfg = U.config([(U.latent(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40), U.dense()),
+                    (U.latent(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=40, kv_from=0), None)], width=64)
+    W = U.weights(cfg, seed=53)
+    a, b = toks(330, seed=33), toks(120, seed=34)
+    wa, wb = U.oracle_logits(cfg, W, a), U.oracle_logits(cfg, W, b)
+    e = U.engine(cfg, W, "bfloat16", pool_tokens=512, page_size=16)
+    f = U.Feeder(e)
+    f.step([("a", a, 280), ("b", b, 70)])
+    f.step([("a", a, 50), ("b", b, 50)])
+    ga, gb = f.end("a"), f.end("b")
+    f.step([("c", a, 200)])
+    f.step([("c", a, 130)])
+    gc = f.end("c")
+    e.close()
+    assert U.bf16_close(ga, wa) and U.bf16_close(gb, wb) and U.bf16_close(gc, wa)
+    assert float(np.median(U.row_errs(ga, wa))) < 2e-2 and float(np.median(U.row_errs(ga, gc))) < 2e-2
+
+
 @pytest.mark.parametrize("experts,top", [(2, 1), (4, 2), (3, 3)])
 def test_large_expert_passes_in_bfloat16_run_one_product_per_expert(experts, top):
     """A pass with at least 64 rows per expert on average sorts its rows by expert and runs each expert's rows as one
