@@ -322,7 +322,7 @@ __global__ void stack_glu_kernel(const float *__restrict__ gu, const float *__re
   const int rows = rows_ptr ? min(M, rows_ptr[0]) : M;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const float *gr = gu + (long long)r * 2 * ff;
-    for (int c = threadIdx.x; c < ff; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
       const float g = fminf(gr[c] + (bias ? bias[c] : 0.f), limit);
       const float u = fminf(fmaxf(gr[ff + c] + (bias ? bias[ff + c] : 0.f), -limit), limit);
       st_el<F32>(act, (long long)r * ff + c, g * sigmoid_precise(1.702f * g) * (u + 1.f));
@@ -332,7 +332,8 @@ __global__ void stack_glu_kernel(const float *__restrict__ gu, const float *__re
 cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
                              cudaStream_t st) {
   if (M <= 0) return cudaSuccess;
-  const int grid = std::min(M, 148 * 16);
+  // few rows: the columns are spread over grid.y as well
+  const dim3 grid(std::min(M, 148 * 16), M >= 512 ? 1 : std::min((ff + 255) / 256, 16));
   if (f32) stack_glu_kernel<true><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
   else stack_glu_kernel<false><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
   return cudaGetLastError();

@@ -481,7 +481,7 @@ cudaError_t launch_stack_latent_prep(const float *proj, long long ld, int q_off,
 // tile against the pair's query (latent part absorbed into the query, rotated part appended), the warp keeps a running maximum
 // that starts at the head's sink and a running denominator that starts at exp(sink - max) = 1, and lanes own coordinates of
 // the output latent.  Per-pair running state lives in shared memory between tiles.
-constexpr int kLatTile = 32, kLatWarps = 8, kLatMaxR = 1024;
+constexpr int kLatTile = 32, kLatWarps = 8, kLatMaxR = 1024, kLatMaxSplit = 64;
 
 int stack_latent_block_tokens(const StackLatent &c) {
   // shared memory: tile [32][D+1] + [warps][32] weights + per pair (D query + r accumulators + 2)
@@ -584,22 +584,27 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
 
 // Merge of the slices: out = sum_s acc_s e^(m_s - M) / (e^(sink - M) + sum_s l_s e^(m_s - M)), M = max(sink, max_s m_s).
 __global__ void stack_latent_merge_kernel(const float *part, const float *sink, int n_split, int pairs_total, int H, int r, float *ol) {
+  __shared__ float ws[kLatMaxSplit];  // per slice e^(m_s - M), 0 for an empty slice
+  __shared__ float inv_den;
   const int p = blockIdx.x;
   const float sk = sink[p % H];
   float M = sk;
   for (int s = 0; s < n_split; s++) M = fmaxf(M, part[((long long)s * pairs_total + p) * (r + 2) + r]);
-  float den = expf(sk - M);
-  for (int s = 0; s < n_split; s++) {
-    const float *rec = part + ((long long)s * pairs_total + p) * (r + 2);
-    if (rec[r] != -INFINITY) den += rec[r + 1] * expf(rec[r] - M);
+  for (int s = threadIdx.x; s < n_split; s += blockDim.x) {
+    const float m = part[((long long)s * pairs_total + p) * (r + 2) + r];
+    ws[s] = m == -INFINITY ? 0.f : expf(m - M);
   }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float den = expf(sk - M);
+    for (int s = 0; s < n_split; s++) den += part[((long long)s * pairs_total + p) * (r + 2) + r + 1] * ws[s];
+    inv_den = 1.f / den;
+  }
+  __syncthreads();
   for (int j = threadIdx.x; j < r; j += blockDim.x) {
     float v = 0.f;
-    for (int s = 0; s < n_split; s++) {
-      const float *rec = part + ((long long)s * pairs_total + p) * (r + 2);
-      if (rec[r] != -INFINITY) v = fmaf(rec[j], expf(rec[r] - M), v);
-    }
-    ol[(long long)p * r + j] = v / den;
+    for (int s = 0; s < n_split; s++) v = fmaf(part[((long long)s * pairs_total + p) * (r + 2) + j], ws[s], v);
+    ol[(long long)p * r + j] = v * inv_den;
   }
 }
 
@@ -659,6 +664,7 @@ cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32
   if (n_qb <= 0) return cudaSuccess;
   if (c.r > kLatMaxR) return cudaErrorInvalidValue;
   if (n_split <= 1 || !part) { n_split = 1; part = nullptr; }
+  if (n_split > kLatMaxSplit) return cudaErrorInvalidValue;
   const int D = c.r + c.dr, bq = stack_latent_block_tokens(c);
   const size_t sh = ((size_t)kLatTile * (D + 1 + kLatWarps) + (size_t)bq * c.H * (D + c.r + 2)) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;

@@ -584,7 +584,7 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
   // latent attention: with few query blocks the history is cut into slices so that about two CTAs per SM run
   stack_lat_split = 1; stack_lat_keys = 0;
   if (QB > 0 && QB < kNumSMs && stack_max_ctx >= 256 && stack_lat_rec) {
-    int sp = std::min(std::min((2 * kNumSMs + QB - 1) / QB, stack_max_ctx / 128), 64);
+    int sp = std::min(std::min((2 * kNumSMs + QB - 1) / QB, stack_max_ctx / 32), 64);  // a slice holds at least one 32-key tile
     const int keys = ((stack_max_ctx + sp - 1) / sp + 31) / 32 * 32;
     sp = (stack_max_ctx + keys - 1) / keys;
     if (sp > 1 && (size_t)sp * T * stack_lat_rec <= M.lat_part_elems) { stack_lat_split = sp; stack_lat_keys = keys; }
