@@ -303,6 +303,68 @@ cudaError_t launch_stack_canon(const float *hn, const float *w, float *state, co
   return cudaGetLastError();
 }
 
+// Passes of single tokens (every span one token long): the whole boundary between two sublayers in one kernel, one block per
+// token.  y = bias + sum of the n_part split-K slices of the product before (slice stride `stride`); x += post * unit_rms(y);
+// hn = pre * unit_rms(x); hc = hn + convolution over the slot's tail and hn; the tail moves on by one.  pre == null: only
+// the residual is updated (end of the pass).  taps == 0: no convolution.
+template <bool F32>
+__global__ void __launch_bounds__(256) stack_boundary_single_kernel(float *x, const float *y, int n_part, long long stride, const float *bias,
+                                                                    const float *post, const float *pre, const float *cw, float *cstate,
+                                                                    StackSpans sp, void *hc, int W, int taps, float eps) {
+  extern __shared__ float row[];  // [W]
+  __shared__ float sh[32];
+  const long long t = blockIdx.x;
+  float *xr = x + t * W;
+  if (y) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = bias ? bias[i] : 0.f;
+      for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
+      row[i] = v;
+      s += v * v;
+    }
+    s = block_sum(s, sh);
+    const float r = rsqrtf(s / (float)W + eps) * post[0];
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = xr[i] + row[i] * r; xr[i] = v; row[i] = v; }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = xr[i];
+  }
+  if (!pre) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i] * row[i];  // each thread re-reads what it wrote itself
+  s = block_sum(s, sh);
+  const float r = rsqrtf(s / (float)W + eps) * pre[0];
+  const int pos = sp.pos[t], slot = sp.slot[t];
+  float *tail = cstate + (long long)slot * (taps > 1 ? taps - 1 : 0) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float h = row[i] * r;
+    float acc = h;
+    if (taps >= 1) {
+      float old[kCanonMaxTaps];
+      for (int j = 0; j < taps - 1; j++) old[j] = pos - (taps - 1 - j) >= 0 ? tail[(long long)j * W + i] : 0.f;
+      for (int j = 0; j < taps - 1; j++) acc = fmaf(cw[(long long)i * taps + j], old[j], acc);
+      acc = fmaf(cw[(long long)i * taps + taps - 1], h, acc);
+      for (int j = 0; j + 2 < taps; j++) tail[(long long)j * W + i] = old[j + 1];
+      if (taps > 1) tail[(long long)(taps - 2) * W + i] = h;
+    }
+    st_el<F32>(hc, t * W + i, acc);
+  }
+}
+cudaError_t launch_stack_boundary_single(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post,
+                                         const float *pre, const float *cw, float *cstate, const StackSpans &sp, void *hc, bool f32,
+                                         int W, int taps, float eps, cudaStream_t st) {
+  if (taps < 0 || taps > kCanonMaxTaps || (size_t)W * 4 > 160 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_boundary_single_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_boundary_single_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  }));
+  const size_t shb = (size_t)W * 4;
+  if (f32) stack_boundary_single_kernel<true><<<sp.T, 256, shb, st>>>(x, y, n_part, stride, bias, post, pre, cw, cstate, sp, hc, W, taps, eps);
+  else stack_boundary_single_kernel<false><<<sp.T, 256, shb, st>>>(x, y, n_part, stride, bias, post, pre, cw, cstate, sp, hc, W, taps, eps);
+  return cudaGetLastError();
+}
+
 template <bool F32>
 __global__ void stack_copy_act_kernel(const float *hn, void *hc, long long n) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)

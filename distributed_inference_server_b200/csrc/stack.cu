@@ -675,6 +675,9 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   StackSpans sp{mt.d<uint32_t>(mt.o_tokens), mt.d<int>(mt.o_pos), mt.d<int>(mt.o_ptrow), mt.d<int>(mt.o_span),
                 mt.d<int>(mt.o_qb_tok0), mt.d<int>(mt.o_qb_len), mt.d<int>(mt.o_qb_pos0), mt.d<int>(mt.o_qb_ptrow), T, n_spans};
   uint64_t &kl = kernel_launches;
+  int pend_parts = 1;  // the product whose result the next boundary consumes: slices left unsummed, their stride, its bias
+  long long pend_stride = 0;
+  const float *pend_bias = nullptr, *pend_src = nullptr;
   pdl_enabled() = false;  // this family's kernels are plain launches: every kernel starts after the one before it has ended
   // Dense projection out[Mrows][N] = A[Mrows][K] W[N][K]^T (+ bias).  bf16 operands go to the tcgen05 product the Llama path
   // uses (fp32 accumulation in TMEM; split-K slices summed, with the bias, by one more kernel); float operands, and shapes a
@@ -682,8 +685,9 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   // later_bias: the caller's next kernel can add the bias itself; it is set to the bias when this product left it out (a
   // single-slice tensor-core product, which has no pass of its own over the result) and to null when it is already in.
   auto gemm = [&](const void *A, bool a_f32, long long lda, const StackTensor &Wt, size_t w_off, const float *bias, float *out,
-                  int Mrows, int N, int K, int a_rows = 0, const float **later_bias = nullptr) -> cudaError_t {
+                  int Mrows, int N, int K, int a_rows = 0, const float **later_bias = nullptr, bool later_sum = false) -> cudaError_t {
     if (later_bias) *later_bias = nullptr;
+    pend_parts = 1; pend_stride = 0; pend_bias = nullptr;
     if (stack_tc && !f32 && !a_f32 && !Wt.f32 && a_rows > 0 && K % 8 == 0 && lda == K && (w_off * 2) % 16 == 0) {
       const TmaMap *xm = stack_map(A, (uint64_t)a_rows, (uint64_t)K, (uint32_t)gemm_token_tile(Mrows));
       const TmaMap *wm = stack_map(reinterpret_cast<const uint16_t *>(Wt.ptr) + w_off, (uint64_t)N, (uint64_t)K, 128);
@@ -695,6 +699,10 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       if (s == 1 && !bias) return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, stream);
       if ((size_t)s * Mrows * N > M.scratch_elems) return cudaErrorInvalidValue;
       RET_CUDA(launch_gemm_partial(*wm, *xm, M.scratch, Mrows, N, K, 0, s, stream));
+      if (later_sum) {  // the boundary kernel of a single-token pass sums the slices and adds the bias
+        pend_parts = s; pend_stride = (long long)Mrows * N; pend_bias = bias; pend_src = M.scratch;
+        return cudaSuccess;
+      }
       kl++;
       return launch_stack_sum_bias(M.scratch, s, (long long)Mrows * N, bias, out, Mrows, N, stream);
     }
@@ -708,7 +716,15 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   };
   RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, T, W, stream)); kl++;
   const float *pend_y = nullptr, *pend_post = nullptr;
+  const bool single = T == n_spans;  // every span one token long: the fused boundary kernel
   auto sublayer_in = [&](const float *pre, const float *cw, float *cstate) -> cudaError_t {
+    if (single) {
+      kl++;
+      const cudaError_t e = launch_stack_boundary_single(M.x, pend_y ? (pend_parts > 1 || pend_bias ? pend_src : pend_y) : nullptr, pend_parts,
+                                                         pend_stride, pend_bias, pend_post, pre, cw, cstate, sp, M.hc, f32, W, taps, eps, stream);
+      pend_y = nullptr; pend_parts = 1; pend_bias = nullptr;
+      return e;
+    }
     RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, pre, M.hn, T, W, eps, stream)); kl++;
     pend_y = nullptr;
     if (taps >= 1) { kl += taps > 1 ? 2 : 1; return launch_stack_canon(M.hn, cw, cstate, sp, M.hc, f32, W, taps, stream); }
@@ -825,7 +841,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       kl += 5;
       n_mix = H * dv;
     }
-    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, nullptr, M.y, T, W, n_mix, cap_tokens));
+    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, nullptr, M.y, T, W, n_mix, cap_tokens, nullptr, single));
     pend_y = M.y; pend_post = L.g4 + 1;
     if (lc.mlp == DIS_MLP_NONE) continue;
     RET_CUDA(sublayer_in(L.g4 + 2, L.canon2, L.cstate2));
@@ -834,7 +850,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       const float *gu_bias = nullptr;
       RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias));
       RET_CUDA(launch_stack_glu(M.proj, gu_bias, M.act, f32, nullptr, T, ff, lc.limit, stream)); kl++;
-      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens));
+      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens, nullptr, single));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
       RET_CUDA(launch_stack_route(M.hc, f32, reinterpret_cast<const float *>(L.router.ptr), T, W, E, top, M.r_idx, M.r_wt, stream));
@@ -893,7 +909,8 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     pend_y = M.y; pend_post = L.g4 + 3;
   }
   // the last sublayer's output joins the residual; rows that need logits get the final norm and the head
-  RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++;
+  if (single) RET_CUDA(sublayer_in(nullptr, nullptr, nullptr));
+  else { RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++; }
   if (R <= 0) return cudaSuccess;
   RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream)); kl++;
   RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W, M.max_rows));

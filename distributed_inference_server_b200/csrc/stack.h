@@ -51,6 +51,10 @@ cudaError_t launch_stack_resid_norm(float *x, const float *y, const float *post,
 // ([slots][taps-1][W]); then the state is replaced by the span's last taps-1 inputs (second launch inside).
 cudaError_t launch_stack_canon(const float *hn, const float *w, float *state, const StackSpans &sp, void *hc, bool f32, int W,
                                int taps, cudaStream_t st);
+// Passes of single tokens: residual update (y given as n_part slices + bias), both norms, convolution and tail update in one kernel
+cudaError_t launch_stack_boundary_single(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post,
+                                         const float *pre, const float *cw, float *cstate, const StackSpans &sp, void *hc, bool f32,
+                                         int W, int taps, float eps, cudaStream_t st);
 cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st);
 // proj [T][ld]: q at 0, k at H*d, v at 2*H*d (pre-activation).  state [slots][H][d][dv].  o [T][H*dv] fp32.
 // seg (or null): room for stack_lightning_seg_floats() floats -- spans longer than stack_lightning_seg_tokens() (max_len: the
