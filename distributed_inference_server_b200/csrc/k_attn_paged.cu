@@ -147,7 +147,7 @@ attn_paged_kernel(const __grid_constant__ CUtensorMap kv_map, long long row0, co
   };
 
   // One stage is kept back for the refill at the top of iteration 0.  Filling the whole ring up front (nothing consumes a
-  // tile before the RoPE prologue is over) was measured in round 2: 3.491 / 3.495 against 3.531 / 3.479 ms per step at
+  // tile before the RoPE prologue is over) was measured: 3.491 / 3.495 against 3.531 / 3.479 ms per step at
   // batch 32, 4.269 against 4.253 at batch 64 -- no gain, not kept.
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages - 1; s++)

@@ -97,7 +97,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     fence_proxy_async();
     // Weights depend neither on the previous kernel nor on this CTA's TMEM allocation: the thread that has just
     // initialised the barriers can fill the ring with weight tiles at once, before the CTA-wide barrier below
-    // (DIS_GEMM_EARLY_TMA=0 keeps the round-1 order for A/B runs)
+    // (DIS_GEMM_EARLY_TMA=0 keeps the earlier order for A/B runs)
     if (early_tma) issue_weights();
   }
   if (warp == 1) tmem_alloc<Cfg::kTmemCols>(tmem_slot);

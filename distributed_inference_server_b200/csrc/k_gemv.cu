@@ -32,7 +32,7 @@ __device__ __forceinline__ float dot8(const uint4 &w, const uint4 &x) {
 // kept full across row groups -- 4.15 ms per step: the per-item bookkeeping and a barrier per row group cost more
 // issue slots than the CTA turnover they remove; 4 rows x depth 4 -- 3.62 ms (fewer CTAs resident); this kernel as ONE
 // wave of CTAs each walking ~13 row groups (so that the dependent kernel is released at once) -- 4.18 ms: without
-// loads in flight across the group boundary the memory pipe idles during every reduction.  Round 2: the residual add +
+// loads in flight across the group boundary the memory pipe idles during every reduction.  Later: the residual add +
 // RMSNorm in front of the QKV / gate-up / lm_head GEMV folded INTO the GEMV (every CTA rebuilds the 8 KB normalised
 // activation for itself from x + the pending output, which removes both norm kernels of a layer) -- 5.46 ms per step
 // against 3.18: 32 KB of L2 reads, two block barriers and an rsqrt in front of every one of 768-16032 short CTAs cost far

@@ -548,9 +548,14 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
       float sc = -INFINITY;
       if (l < nk && k0 + l <= qpos) {
         const float *kr = tile + (size_t)l * DP;
-        float s = 0.f;
-        for (int i = 0; i < D; i++) s = fmaf(q[i], kr[i], s);
-        sc = s * c.scale;
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // four chains, added at the end: the sum's order is fixed by D alone
+        int i = 0;
+        for (; i + 3 < D; i += 4) {
+          s0 = fmaf(q[i], kr[i], s0); s1 = fmaf(q[i + 1], kr[i + 1], s1);
+          s2 = fmaf(q[i + 2], kr[i + 2], s2); s3 = fmaf(q[i + 3], kr[i + 3], s3);
+        }
+        for (; i < D; i++) s0 = fmaf(q[i], kr[i], s0);
+        sc = ((s0 + s1) + (s2 + s3)) * c.scale;
       }
       const float m_old = mx[p];
       const float m_new = fmaxf(m_old, warp_max(sc));
@@ -562,9 +567,14 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
       pw[l] = pr;
       __syncwarp();
       for (int j = l; j < r; j += 32) {
-        float v = a[j] * corr;
-        for (int kk = 0; kk < nk; kk++) v = fmaf(pw[kk], tile[(size_t)kk * DP + j], v);
-        a[j] = v;
+        float v0 = a[j] * corr, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+        int kk = 0;
+        for (; kk + 3 < nk; kk += 4) {
+          v0 = fmaf(pw[kk], tile[(size_t)kk * DP + j], v0); v1 = fmaf(pw[kk + 1], tile[(size_t)(kk + 1) * DP + j], v1);
+          v2 = fmaf(pw[kk + 2], tile[(size_t)(kk + 2) * DP + j], v2); v3 = fmaf(pw[kk + 3], tile[(size_t)(kk + 3) * DP + j], v3);
+        }
+        for (; kk < nk; kk++) v0 = fmaf(pw[kk], tile[(size_t)kk * DP + j], v0);
+        a[j] = (v0 + v1) + (v2 + v3);
       }
       __syncwarp();
       if (l == 0) { mx[p] = m_new; dn[p] = dn[p] * corr + psum; }

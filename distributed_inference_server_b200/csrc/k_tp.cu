@@ -13,7 +13,7 @@
 //   tp_add_rmsnorm_kernel     one-shot push, one flag hop                       (tp-1)   * T*H*4 bytes per rank
 //   tp_add_rmsnorm2_kernel    reduce-scatter + all-gather of column blocks      2(tp-1)/tp * T*H*4, two flag hops
 //   tp_add_rmsnorm_ll_kernel  the same two hops with the flag inside the data   4(tp-1)/tp * T*H*4, no fence, no flag
-//                             (round 1 default: 3.28 / 2.64 / 2.42 ms per step at TP = 2 / 4 / 8, batch 64)
+//                             (first default: 3.28 / 2.64 / 2.42 ms per step at TP = 2 / 4 / 8, batch 64)
 //   tp_add_rmsnorm_wide_kernel  the ll protocol on a (row, column block) grid that covers every SM (see below)
 //
 // The first is a one-shot all-reduce: every rank sends (tp-1) * T * H * 4 bytes; no NVLink round trip is on the

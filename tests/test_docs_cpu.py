@@ -44,7 +44,7 @@ def test_every_cited_profile_file_exists():
 
 
 def test_profiles_index_covers_the_directory():
-    """profiles/README.md names every round-2 file of the directory (directly, by brace alternative or by wildcard)."""
+    """profiles/README.md names every `r2_` file of the directory (directly, by brace alternative or by wildcard)."""
     named = set()
     for path in _cited("profiles/README.md"):
         named.update(os.path.basename(p) for p in glob.glob(os.path.join(ROOT, path)))
