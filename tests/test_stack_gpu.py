@@ -98,12 +98,13 @@ def test_portions_of_several_sizes(sizes):
     assert U.rel_err(got, U.run_whole(cfg, W, t)) < SAME
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 16), (1, 72, 40), (3, 128, 128)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 16), (1, 72, 40), (3, 128, 128), (1, 136, 144)])
 def test_long_recurrent_spans_run_as_segments_with_a_carry(heads, dim, vdim):
     """A span longer than a segment (64 tokens) of the decayed linear-attention scan, or of the gated recurrence, is cut into
     segments that run side by side and are joined by a carry pass.  Spans of one token, of exactly one or two segments, with a
     ragged last segment and with a start in the middle of a sequence share passes here; all must agree with the oracle and
-    with token-by-token feeding."""
+    with token-by-token feeding.  The last size is beyond what the register kernel holds (128 x 128 per head) and runs on the
+    kernel that keeps the state in shared memory."""
     cfg = U.config([(U.lightning(heads=heads, dim=dim, vdim=vdim, decay=[0.999, 0.93, 0.5][:heads]), None), (U.mingru(24), None)],
                    width=40)
     W = U.weights(cfg, seed=61)
@@ -164,12 +165,17 @@ def test_long_portions_in_bfloat16_take_the_matrix_product_path():
     assert float(np.median(U.row_errs(ga, wa))) < 2e-2
 
 
-def test_passes_of_256_tokens_in_bfloat16_run_the_head_products_on_tensor_cores():
+@pytest.mark.parametrize("big", [False, True])
+def test_passes_of_256_tokens_in_bfloat16_run_the_head_products_on_tensor_cores(big):
     """From 256 tokens in a pass, the query absorption and the value expansion of latent attention run as one tensor-core
     product per head over that head's rows packed together (bfloat16; dim, kv_rank and kv_rank + rot_dim multiples of 8).
     A pass above and one below that size, two sequences in one pass, against the oracle and against each other."""
-    cfg = U.config([(U.latent(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40), U.dense()),
-                    (U.latent(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=40, kv_from=0), None)], width=64)
+    if big:  # more than one 64-wide K block and more than one 128-row weight tile in every product
+        cfg = U.config([(U.latent(heads=4, dim=72, rot_dim=32, vdim=136, kv_rank=160), U.dense(ff=96)),
+                        (U.latent(heads=2, dim=136, rot_dim=32, vdim=64, kv_rank=160, kv_from=0), None)], width=192)
+    else:
+        cfg = U.config([(U.latent(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40), U.dense()),
+                        (U.latent(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=40, kv_from=0), None)], width=64)
     W = U.weights(cfg, seed=53)
     a, b = toks(330, seed=33), toks(120, seed=34)
     wa, wb = U.oracle_logits(cfg, W, a), U.oracle_logits(cfg, W, b)
