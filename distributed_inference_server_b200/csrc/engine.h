@@ -171,6 +171,7 @@ struct Engine {
   std::vector<StackSpanH> stack_spans_h;  // spans of the pass being built; products: its latent attention runs as matrix products
   int stack_lat_split = 1, stack_lat_keys = 0;  // slicing of the history in latent attention for the pass being built
   int stack_lat_heads = 0;    // most heads of a latent layer
+  bool stack_lat_mma = false; // some latent layer runs the mma.sync attention kernel (64-key tiles)
   int stack_max_ctx = 0;      // longest history (tokens in the cache after the pass) among the sequences of the pass being built
   size_t stack_lat_rec = 0;   // floats of one token's slice record in split latent attention: max over layers of heads * (kv_rank + 2)
   bool stack_tc = true;  // bf16 dense projections on the tcgen05 GEMM (DIS_STACK_TC=0: the fp32-FMA product everywhere, A/B runs)

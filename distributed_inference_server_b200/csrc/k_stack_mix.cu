@@ -592,6 +592,182 @@ __global__ void __launch_bounds__(kLatWarps * 32) stack_latent_attn_kernel(const
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) { rec[(long long)i * (r + 2) + r] = mx[i]; rec[(long long)i * (r + 2) + r + 1] = dn[i]; }
 }
 
+// ---- the same attention on mma.sync (bf16 compute type, kv_rank a multiple of 8, kv_rank + rot_dim a multiple of 16, at most 16
+// (token, head) pairs per query block): the pairs are the 16 rows of m16n8k16 products.  A CTA stages 64 latents of its slice
+// as bf16, warp w scores keys 8w .. 8w+7 against all pairs (K = kv_rank + rot_dim), the scores go through shared memory for the
+// online softmax (fp32, two rows per warp, starting at the sink as above), and each warp then adds P C into the output
+// coordinates it owns (n-tiles w, w + 8, ...), which stay in registers over the whole slice.
+__device__ __forceinline__ void mma_bf16_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+constexpr int kMmaKeys = 64, kMmaRows = 16, kMmaPS = 72;
+bool stack_latent_mma_ok(const StackLatent &c, bool f32) {
+  return !f32 && c.r % 8 == 0 && (c.r + c.dr) % 16 == 0 && c.r <= kLatMaxR && c.H <= kMmaRows;
+}
+static size_t latent_mma_smem(const StackLatent &c) {
+  const size_t DS = (size_t)c.r + c.dr + 8;
+  return (kMmaRows + kMmaKeys) * DS * 2 + (size_t)kMmaRows * kMmaKeys * 4 + (size_t)kMmaRows * kMmaPS * 2 + 4 * kMmaRows * 4;
+}
+template <int NTW>
+__global__ void __launch_bounds__(256) stack_latent_attn_mma_kernel(const float *qf, const uint16_t *pool, const float *sink, StackLatent c,
+                                                                    StackSpans sp, const int *qb_tok0, const int *qb_len,
+                                                                    const int *page_table, int max_pages, int page_size, float *ol,
+                                                                    int keys_per_split, float *part) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int D = c.r + c.dr, r = c.r, DS = D + 8;
+  uint16_t *qs = reinterpret_cast<uint16_t *>(smraw);                  // [16][DS]
+  uint16_t *tile = qs + (size_t)kMmaRows * DS;                         // [64][DS]
+  float *S = reinterpret_cast<float *>(tile + (size_t)kMmaKeys * DS);  // [16][64]
+  uint16_t *P = reinterpret_cast<uint16_t *>(S + kMmaRows * kMmaKeys); // [16][72]
+  float *mx = reinterpret_cast<float *>(P + kMmaRows * kMmaPS);        // [16]
+  float *dn = mx + kMmaRows, *cr = dn + kMmaRows;                      // [16] each
+  int *qp = reinterpret_cast<int *>(cr + kMmaRows);                    // [16] position of the row's query, -1 for a padding row
+  __shared__ long long prow_s[kMmaKeys];
+  const int tok0 = qb_tok0[blockIdx.x], nq = qb_len[blockIdx.x];
+  const int pairs = nq * c.H;
+  if (pairs > kMmaRows) return;  // the host cuts query blocks to fit
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, g = l >> 2, tig = l & 3;
+  const int slot = sp.slot[tok0];
+  const int last_pos = sp.pos[tok0 + nq - 1];
+  {  // queries: four floats per load, four loads in flight per thread before the first is converted and stored
+    const int n4 = kMmaRows * D / 4;
+    const float4 *src = reinterpret_cast<const float4 *>(qf + (long long)tok0 * c.H * D);
+    for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * blockDim.x;
+        v[u] = (i < n4 && i * 4 < pairs * D) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * blockDim.x;
+        if (i < n4) {
+          const int row = (i * 4) / D, col = i * 4 - row * D;
+          *reinterpret_cast<uint2 *>(qs + (size_t)row * DS + col) = make_uint2(float2_to_bf16x2(v[u].x, v[u].y), float2_to_bf16x2(v[u].z, v[u].w));
+        }
+      }
+    }
+  }
+  if (threadIdx.x < kMmaRows) {
+    const int row = threadIdx.x;
+    mx[row] = part ? -INFINITY : (row < pairs ? sink[row % c.H] : 0.f);
+    dn[row] = part ? 0.f : 1.f;
+    qp[row] = row < pairs ? sp.pos[tok0 + row / c.H] : -1;
+  }
+  float acc[NTW][4];
+#pragma unroll
+  for (int nt = 0; nt < NTW; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  const int *pt = page_table + (long long)slot * max_pages;
+  const int k_begin = part ? (int)blockIdx.y * keys_per_split : 0;
+  const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
+  const int vpr = D >> 3;
+  for (int k0 = k_begin; k0 < k_end; k0 += kMmaKeys) {
+    const int nk = min(kMmaKeys, k_end - k0);
+    __syncthreads();
+    if (threadIdx.x < kMmaKeys) {  // pool row of every key of the tile, so that the loads below do not wait on the page table
+      const int kp = k0 + threadIdx.x;
+      prow_s[threadIdx.x] = threadIdx.x < nk ? (long long)pt[kp / page_size] * page_size + kp % page_size : -1;
+    }
+    __syncthreads();
+    for (int i0 = threadIdx.x; i0 < kMmaKeys * vpr; i0 += 6 * blockDim.x) {
+      uint4 v[6];
+#pragma unroll
+      for (int u = 0; u < 6; u++) {
+        const int i = i0 + u * blockDim.x;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);  // rows past the slice's end are zero: their weights are zero too
+        if (i < kMmaKeys * vpr) {
+          const int kk = i / vpr, cv = i - kk * vpr;
+          const long long prow = prow_s[kk];
+          if (prow >= 0) v[u] = *reinterpret_cast<const uint4 *>(pool + prow * D + cv * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 6; u++) {
+        const int i = i0 + u * blockDim.x;
+        if (i < kMmaKeys * vpr) {
+          const int kk = i / vpr, cv = i - kk * vpr;
+          *reinterpret_cast<uint4 *>(tile + (size_t)kk * DS + cv * 8) = v[u];
+        }
+      }
+    }
+    __syncthreads();
+    {  // scores of keys 8w .. 8w+7
+      float sa[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint16_t *qa = qs + (size_t)g * DS + 2 * tig, *qb = qs + (size_t)(g + 8) * DS + 2 * tig;
+      const uint16_t *kb = tile + (size_t)(w * 8 + g) * DS + 2 * tig;
+      for (int k = 0; k < D; k += 16) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(qa + k), a1 = *reinterpret_cast<const uint32_t *>(qb + k);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t *>(qa + k + 8), a3 = *reinterpret_cast<const uint32_t *>(qb + k + 8);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kb + k), b1 = *reinterpret_cast<const uint32_t *>(kb + k + 8);
+        mma_bf16_m16n8k16(sa, a0, a1, a2, a3, b0, b1);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int row = g + (e >> 1) * 8, col = w * 8 + 2 * tig + (e & 1);
+        const bool seen = col < nk && k0 + col <= qp[row];
+        S[row * kMmaKeys + col] = seen ? sa[e] * c.scale : -INFINITY;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int rr = 0; rr < 2; rr++) {
+      const int row = 2 * w + rr;
+      const float s0 = S[row * kMmaKeys + l], s1 = S[row * kMmaKeys + l + 32];
+      const float m_old = mx[row];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+      const float p0 = s0 == -INFINITY ? 0.f : expf(s0 - m_new), p1 = s1 == -INFINITY ? 0.f : expf(s1 - m_new);
+      const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+      const float psum = warp_sum(p0 + p1);
+      P[row * kMmaPS + l] = float_to_bf16_bits(p0);
+      P[row * kMmaPS + l + 32] = float_to_bf16_bits(p1);
+      __syncwarp();
+      if (l == 0) { mx[row] = m_new; dn[row] = dn[row] * corr + psum; cr[row] = corr; }
+    }
+    __syncthreads();
+    const float c_lo = cr[g], c_hi = cr[g + 8];
+#pragma unroll
+    for (int nt = 0; nt < NTW; nt++) { acc[nt][0] *= c_lo; acc[nt][1] *= c_lo; acc[nt][2] *= c_hi; acc[nt][3] *= c_hi; }
+    const int ksteps = (nk + 15) >> 4;
+    for (int ks = 0; ks < ksteps; ks++) {
+      const int kk = ks * 16;
+      const uint32_t a0 = *reinterpret_cast<const uint32_t *>(P + g * kMmaPS + kk + 2 * tig);
+      const uint32_t a1 = *reinterpret_cast<const uint32_t *>(P + (g + 8) * kMmaPS + kk + 2 * tig);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t *>(P + g * kMmaPS + kk + 8 + 2 * tig);
+      const uint32_t a3 = *reinterpret_cast<const uint32_t *>(P + (g + 8) * kMmaPS + kk + 8 + 2 * tig);
+      const uint16_t *t0 = tile + (size_t)(kk + 2 * tig) * DS + g;
+#pragma unroll
+      for (int nt = 0; nt < NTW; nt++) {
+        const int n0 = (w + nt * 8) * 8;
+        if (n0 < r) {
+          const uint32_t b0 = (uint32_t)t0[n0] | ((uint32_t)t0[n0 + DS] << 16);
+          const uint32_t b1 = (uint32_t)t0[n0 + 8 * (size_t)DS] | ((uint32_t)t0[n0 + 9 * (size_t)DS] << 16);
+          mma_bf16_m16n8k16(acc[nt], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int nt = 0; nt < NTW; nt++) {
+    const int n0 = (w + nt * 8) * 8;
+    if (n0 >= r) continue;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int row = g + (e >> 1) * 8, col = n0 + 2 * tig + (e & 1);
+      if (row >= pairs) continue;
+      if (!part) ol[((long long)tok0 * c.H + row) * r + col] = acc[nt][e] / dn[row];
+      else part[((long long)blockIdx.y * sp.T * c.H + (long long)tok0 * c.H + row) * (r + 2) + col] = acc[nt][e];
+    }
+  }
+  if (part && threadIdx.x < pairs) {
+    float *rec = part + ((long long)blockIdx.y * sp.T * c.H + (long long)tok0 * c.H + threadIdx.x) * (r + 2);
+    rec[r] = mx[threadIdx.x]; rec[r + 1] = dn[threadIdx.x];
+  }
+}
+
 // Merge of the slices: out = sum_s acc_s e^(m_s - M) / (e^(sink - M) + sum_s l_s e^(m_s - M)), M = max(sink, max_s m_s).
 __global__ void stack_latent_merge_kernel(const float *part, const float *sink, int n_split, int pairs_total, int H, int r, float *ol) {
   __shared__ float ws[kLatMaxSplit];  // per slice e^(m_s - M), 0 for an empty slice
@@ -675,6 +851,23 @@ cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32
   if (c.r > kLatMaxR) return cudaErrorInvalidValue;
   if (n_split <= 1 || !part) { n_split = 1; part = nullptr; }
   if (n_split > kLatMaxSplit) return cudaErrorInvalidValue;
+  static int use_mma = -1;
+  if (use_mma < 0) { const char *e = getenv("DIS_STACK_LATENT_MMA"); use_mma = (e && atoi(e) == 0) ? 0 : 1; }
+  if (use_mma && stack_latent_mma_ok(c, f32)) {
+    const size_t shm = latent_mma_smem(c);
+    static DeviceOnce once_mma;
+    DIS_CUDA_TRY(once_mma.run([&] {
+      cudaError_t e = cudaFuncSetAttribute(stack_latent_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_latent_attn_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    }));
+    if (shm > 220 * 1024) return cudaErrorInvalidValue;
+    const dim3 grid(n_qb, n_split);
+    const uint16_t *pl = reinterpret_cast<const uint16_t *>(pool);
+    if (c.r <= 512) stack_latent_attn_mma_kernel<8><<<grid, 256, shm, st>>>(qf, pl, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol, keys_per_split, part);
+    else stack_latent_attn_mma_kernel<16><<<grid, 256, shm, st>>>(qf, pl, sink, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, ol, keys_per_split, part);
+    if (part) stack_latent_merge_kernel<<<sp.T * c.H, 128, 0, st>>>(part, sink, n_split, sp.T * c.H, c.H, c.r, ol);
+    return cudaGetLastError();
+  }
   const int D = c.r + c.dr, bq = stack_latent_block_tokens(c);
   const size_t sh = ((size_t)kLatTile * (D + 1 + kLatWarps) + (size_t)bq * c.H * (D + c.r + 2)) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;

@@ -134,6 +134,11 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       if (((size_t)32 * (lc.kv_rank + lc.rot_dim + 9) + (size_t)lc.heads * (2 * lc.kv_rank + lc.rot_dim + 2)) * 4 > 200 * 1024)
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "heads * kv_rank does not fit shared memory");
       stack_bq = std::min(stack_bq, stack_latent_block_tokens(sl));
+      const char *mma_env = getenv("DIS_STACK_LATENT_MMA");
+      if (!(mma_env && atoi(mma_env) == 0) && stack_latent_mma_ok(sl, sc->compute_dtype == DIS_F32)) {
+        stack_bq = std::min(stack_bq, std::max(1, 16 / lc.heads));
+        stack_lat_mma = true;
+      }
     } else return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown mixer");
     if (lc.mlp == DIS_MLP_DENSE) { if (lc.ff <= 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "ff"); }
     else if (lc.mlp == DIS_MLP_MOE) {
@@ -584,7 +589,7 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
   // latent attention: with few query blocks the history is cut into slices so that about two CTAs per SM run
   stack_lat_split = 1; stack_lat_keys = 0;
   if (QB > 0 && QB < kNumSMs && stack_max_ctx >= 256 && stack_lat_rec) {
-    int sp = std::min(std::min((2 * kNumSMs + QB - 1) / QB, stack_max_ctx / 32), 64);  // a slice holds at least one 32-key tile
+    int sp = std::min(std::min((2 * kNumSMs + QB - 1) / QB, stack_max_ctx / (stack_lat_mma ? 64 : 32)), 64);  // a slice holds at least one tile of keys
     const int keys = ((stack_max_ctx + sp - 1) / sp + 31) / 32 * 32;
     sp = (stack_max_ctx + keys - 1) / keys;
     if (sp > 1 && (size_t)sp * T * stack_lat_rec <= M.lat_part_elems) { stack_lat_split = sp; stack_lat_keys = keys; }

@@ -91,6 +91,9 @@ cudaError_t launch_stack_latent_prep(const float *proj, long long ld, int q_off,
 // n_split > 1: the history is cut into slices of keys_per_split keys (a multiple of 32), one CTA per (block, slice), whose
 // records ([n_split][T*H][r+2] floats in `part`) a second kernel merges -- few query blocks then still fill the GPU.
 int stack_latent_block_tokens(const StackLatent &c);
+// the mma.sync form of the kernel applies (bf16, kv_rank % 8 == 0, (kv_rank + rot_dim) % 16 == 0, heads <= 16): query blocks
+// then hold at most 16 (token, head) pairs
+bool stack_latent_mma_ok(const StackLatent &c, bool f32);
 cudaError_t launch_stack_latent_attn(const float *qf, const void *pool, bool f32, const float *sink, const StackLatent &c,
                                      const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb,
                                      const int *page_table, int max_pages, int page_size, float *ol, int n_split,

@@ -165,6 +165,31 @@ def test_long_portions_in_bfloat16_take_the_matrix_product_path():
     assert float(np.median(U.row_errs(ga, wa))) < 2e-2
 
 
+@pytest.mark.parametrize("heads", [1, 2, 5, 16])
+def test_short_portions_and_decoding_in_bfloat16_on_the_tensor_core_attention_kernel(heads):
+    """bfloat16 with kv_rank a multiple of 8 and kv_rank + rot_dim a multiple of 16: portions below 32 tokens and single tokens
+    run latent attention with the (token, head) pairs as the rows of tensor-core tiles over 64 latents at a time; beyond 256
+    tokens of history the history is cut into slices that a merge kernel joins.  Query blocks of several tokens (few heads),
+    of one token (16 heads), ragged last tiles, and a second sequence in the same passes."""
+    cfg = U.config([(U.latent(heads=heads, dim=8, rot_dim=8, vdim=8, kv_rank=40), U.dense()),
+                    (U.latent(heads=3, dim=8, rot_dim=8, vdim=16, kv_rank=40, kv_from=0), None)], width=64)
+    W = U.weights(cfg, seed=71)
+    a, b = toks(345, seed=51), toks(100, seed=52)
+    wa, wb = U.oracle_logits(cfg, W, a), U.oracle_logits(cfg, W, b)
+    e = U.engine(cfg, W, "bfloat16", pool_tokens=512, page_size=16)
+    f = U.Feeder(e)
+    f.step([("a", a, 21), ("b", b, 1)])
+    f.step([("a", a, 31), ("b", b, 30)])
+    f.step([("a", a, 230), ("b", b, 9)])       # a: the matrix-product path; b: short
+    for _ in range(30):                        # a decodes past 256 tokens of history (sliced), b stays below
+        f.step([("a", a, 1), ("b", b, 2)])
+    f.step([("a", a, 33)])
+    ga, gb = f.end("a"), f.end("b")
+    e.close()
+    assert U.bf16_close(ga, wa) and U.bf16_close(gb, wb)
+    assert float(np.median(U.row_errs(ga, wa))) < 2e-2 and float(np.median(U.row_errs(gb, wb))) < 2e-2
+
+
 @pytest.mark.parametrize("big", [False, True])
 def test_passes_of_256_tokens_in_bfloat16_run_the_head_products_on_tensor_cores(big):
     """From 256 tokens in a pass, the query absorption and the value expansion of latent attention run as one tensor-core
