@@ -768,7 +768,7 @@ def run_kidolorn(args):
         moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
         kinds = {"lightning": {"type": "lightning", "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": [0.99] * H}},
                  "latent": lat(), "mingru": {"type": "mingru", "mixer": {"width": W}}}
-        variants = {"mixed": [("lightning", dense), ("latent", moe), ("latent_shared", dense), ("mingru", moe)]}
+        variants = {"mixed": [("latent", dense), ("mingru", moe), ("lightning", dense), ("latent_shared", moe)]}
         if args.per_mixer:
             variants.update({m: [(m, dense)] * 4 for m in kinds})
             variants["latent_moe"] = [("latent", moe)] * 4

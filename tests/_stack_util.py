@@ -25,15 +25,15 @@ def latent(heads=2, dim=8, rot_dim=4, vdim=12, kv_rank=16, kv_from=None, rot_dim
     return {"type": "latent_attention", "mixer": mx}
 
 
-def dense(ff=24, limit=2.0):
+def dense(ff=24, limit=2.5):
     return {"kind": "dense", "ff": ff, "limit": limit}
 
 
-def moe(ff=12, experts=4, top=2, limit=1.5):
+def moe(ff=12, experts=4, top=2, limit=1.25):
     return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
 
 
-def config(layers, vocab=50, width=32, taps=3, eps=1e-5):
+def config(layers, vocab=50, width=32, taps=2, eps=1e-6):
     """layers: list of (mixer dict, mlp dict or None)."""
     cfg = {"architecture": "Kidolorn", "vocab": vocab, "width": width, "norm": {"eps": eps},
            "layers": [dict(m, mlp=f) for m, f in layers]}

@@ -35,18 +35,19 @@ def write_safetensors(path, tensors):
         f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))
 
 
-CFG = U.config([(U.lightning(heads=3, dim=4, vdim=8), U.dense(ff=20, limit=0.75)), (U.latent(), U.moe(ff=6, experts=5, top=3)),
-                (U.latent(kv_from=1, vdim=6), None), (U.mingru(28), U.moe())], vocab=77, width=24, taps=2, eps=3e-4)
+CFG = U.config([(U.latent(), U.moe(ff=6, experts=5, top=3)), (U.mingru(28), U.moe()),
+                (U.lightning(heads=3, dim=4, vdim=8), U.dense(ff=20, limit=0.75)), (U.latent(kv_from=0, vdim=6), None)],
+               vocab=77, width=24, taps=2, eps=3e-4)
 
 
 def test_config_reader_takes_every_size_and_constant_from_the_file():
     s = models.kidolorn_spec(CFG)
     assert (s.vocab, s.width, s.canon_taps, len(s.layers)) == (77, 24, 2, 4) and abs(s.norm_eps - 3e-4) < 1e-12
-    a, b, c, d = s.layers
+    b, d, a, c = s.layers
     assert (a.mixer, a.heads, a.dim, a.vdim, a.mlp, a.ff, a.limit) == ("lightning", 3, 4, 8, "dense", 20, 0.75) and len(a.decay) == 3
     assert (b.mixer, b.kv_rank, b.rot_dim, b.rot_dims, b.kv_from, b.mlp, b.experts, b.top, b.ff) == ("latent_attention", 16, 4, 4, -1, "moe", 5, 3, 6)
-    assert (c.kv_from, c.vdim, c.mlp) == (1, 6, "none")
-    assert (d.mixer, d.width, d.limit) == ("mingru", 28, 1.5)
+    assert (c.kv_from, c.vdim, c.mlp) == (0, 6, "none")
+    assert (d.mixer, d.width, d.limit) == ("mingru", 28, 1.25)
     assert models.kidolorn_spec(U.config([(U.mingru(), None)], taps=0)).canon_taps == 0
 
 
@@ -54,7 +55,7 @@ def test_tensor_table_is_what_the_plain_implementation_reads():
     """The oracle runs on exactly the tensors the table names (a missing one raises KeyError, shapes must multiply)."""
     W = U.weights(CFG, seed=1)
     names = set(models.kidolorn_spec(CFG).tensor_shapes())
-    assert "l2.mix.dkv" not in names and "l1.mix.dkv" in names and "l2.norm2" not in names and "l3.mlp.e3.down" in names
+    assert "l3.mix.dkv" not in names and "l0.mix.dkv" in names and "l3.norm2" not in names and "l1.mlp.e3.down" in names
     out = KO.forward(CFG, {k: torch.from_numpy(v.copy()) for k, v in W.items()}, [1, 2, 3, 4, 5])
     assert out.shape == (5, 77) and bool(torch.isfinite(out).all())
 

@@ -56,8 +56,8 @@ def test_residual_stream_after_every_layer_matches():
         assert U.rel_err(U.run_whole(cfg, W, t), U.oracle_logits(cfg, W, t)) < F32_TOL, n
 
 
-FULL = [(U.lightning(), U.dense()), (U.latent(), U.moe()), (U.latent(kv_from=1), U.dense()), (U.mingru(), U.moe()),
-        (U.latent(heads=1, dim=16, rot_dim=8, vdim=8, kv_rank=8), None)]
+FULL = [(U.mingru(), U.moe()), (U.latent(), U.dense()), (U.lightning(), U.moe()), (U.latent(kv_from=1), None),
+        (U.latent(heads=1, dim=16, rot_dim=8, vdim=8, kv_rank=8), U.dense())]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
