@@ -34,19 +34,28 @@ class EngineConfig(C.Structure):
                 ("eos_token", C.c_int32), ("stream", C.c_void_p), ("nccl_id", C.c_uint8 * 128)]
 
 
-MIX_LIGHTNING, MIX_MINGRU, MIX_LATENT = range(3)
+MIX_LIGHTNING, MIX_MINGRU, MIX_LATENT, MIX_ATTENTION, MIX_PARALLEL = range(5)
 MLP_NONE, MLP_DENSE, MLP_MOE = range(3)
+ACT_CLAMPED, ACT_GELU_TANH = range(2)
+NORM_RMS_SCALAR, NORM_LAYER = range(2)
+ATTN_SIGMOID, ATTN_QK_NORM, ATTN_V_IS_K, ATTN_ROT_V, ATTN_BIAS = 1, 2, 4, 8, 16
 
 
 class LayerConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "dim", "vdim", "width", "kv_rank", "rot_dim", "rot_dims", "kv_from")] + \
                [("rot_base", C.c_float), ("scale", C.c_float), ("decay", C.POINTER(C.c_float))] + \
-               [(n, C.c_int32) for n in ("mlp", "ff", "experts", "top")] + [("limit", C.c_float)]
+               [(n, C.c_int32) for n in ("mlp", "ff", "experts", "top")] + [("limit", C.c_float)] + \
+               [("kv_heads", C.c_int32), ("attn_flags", C.c_uint32), ("rot_factor", C.c_float), ("rot_low", C.c_float),
+                ("rot_high", C.c_float), ("rot_original", C.c_int32)] + \
+               [(n, C.c_int32) for n in ("gla_heads", "gla_dim", "gla_vdim", "gla_rank")] + \
+               [("gla_tau", C.c_float), ("mix_scale", C.c_float), ("gla_scale", C.c_float), ("mlp_act", C.c_int32)]
 
 
 class StackConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "width", "n_layers", "canon_taps", "max_ctx", "max_logit_rows", "compute_dtype")] + \
-               [("norm_eps", C.c_float), ("layers", C.POINTER(LayerConfig))]
+               [("norm_eps", C.c_float), ("layers", C.POINTER(LayerConfig))] + \
+               [("norm_kind", C.c_int32), ("embed_scale", C.c_float), ("logit_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times")]
 
 
 class SamplingParams(C.Structure):

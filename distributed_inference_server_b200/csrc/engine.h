@@ -60,7 +60,7 @@ struct StepMeta {
   size_t o_tokens, o_pos, o_ptrow, o_ctx, o_rowmap, o_temp, o_topp, o_seed, o_step;
   size_t o_qb_tok0, o_qb_len, o_qb_pos0, o_qb_ptrow;  // prefill query blocks
   size_t o_arstep;                                     // forward-pass counter (epoch of the peer-memory exchange)
-  size_t o_span = 0, o_ab_tok0 = 0, o_ab_len = 0;       // layer-list family: span of each token; attention query blocks
+  size_t o_span = 0, o_ab_tok0 = 0, o_ab_len = 0, o_kb_tok0 = 0, o_kb_len = 0;       // layer-list family: span of each token; attention query blocks
   template <class T_> T_ *h(size_t off) { return reinterpret_cast<T_ *>(host + off); }
   template <class T_> T_ *d(size_t off) { return reinterpret_cast<T_ *>(dev + off); }
 };
@@ -163,13 +163,20 @@ struct Engine {
   // layer-list decoders (stack.cu): the same sequences, pages, planner and sampler; prompt = the whole token history
   StackModel *stack = nullptr;
   std::vector<void *> stack_allocs;
-  struct StackTarget { StackTensor *dst; size_t off; std::vector<int64_t> shape; int transform; bool loaded; int layer; };
+  // transform 1: latent key up-projection, each head's [d][r] block transposed; 2: a block of columns of a wider matrix
+  // (row stride ld, first column off)
+  struct StackTarget { StackTensor *dst; size_t off; std::vector<int64_t> shape; int transform; bool loaded; int layer; long long ld = 0; };
   std::map<std::string, StackTarget> stack_names;
   int stack_bq = 8;
   bool stack_capturing = false;  // a decode pass is being captured: nothing in it may wait for the device
   struct StackSpanH { int tok0, len, pos0, slot; bool products; };
   std::vector<StackSpanH> stack_spans_h;  // spans of the pass being built; products: its latent attention runs as matrix products
   int stack_lat_split = 1, stack_lat_keys = 0;  // slicing of the history in latent attention for the pass being built
+  int stack_abq = 0;          // tokens per query block of paged attention (0: the model has none); smallest over its layers
+  int stack_kb = 0;           // its query blocks in the pass being built
+  int stack_att_split = 1, stack_att_keys = 0;  // its slicing of the history
+  int stack_att_heads = 0, stack_att_groups = 0;  // most query heads, fewest key/value heads of an attention layer
+  size_t stack_att_rec = 0;   // floats of one token's slice record: max over layers of heads * (vdim + 2)
   int stack_lat_heads = 0;    // most heads of a latent layer
   bool stack_lat_mma = false; // some latent layer runs the mma.sync attention kernel (64-key tiles)
   int stack_max_ctx = 0;      // longest history (tokens in the cache after the pass) among the sequences of the pass being built

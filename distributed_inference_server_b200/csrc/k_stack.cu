@@ -194,14 +194,19 @@ cudaError_t launch_stack_sum_bias(const float *part, int n_part, long long strid
 
 // ------------------------------------------------------------------------------------------------ embedding, norms
 template <bool F32>
-__global__ void stack_embed_kernel(const void *embed, const uint32_t *tokens, float *x, int W) {
+__global__ void stack_embed_kernel(const void *embed, const uint32_t *tokens, float *x, float *x0, float scale, int W) {
   const long long t = blockIdx.x;
   const long long row = tokens[t];
-  for (int i = threadIdx.x; i < W; i += blockDim.x) x[t * W + i] = ld_el<F32>(embed, row * W + i);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = ld_el<F32>(embed, row * W + i) * scale;
+    x[t * W + i] = v;
+    if (x0) x0[t * W + i] = v;
+  }
 }
-cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, int T, int W, cudaStream_t st) {
-  if (f32) stack_embed_kernel<true><<<T, 128, 0, st>>>(embed, tokens, x, W);
-  else stack_embed_kernel<false><<<T, 128, 0, st>>>(embed, tokens, x, W);
+cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, float *x0, float scale, int T, int W,
+                               cudaStream_t st) {
+  if (f32) stack_embed_kernel<true><<<T, 128, 0, st>>>(embed, tokens, x, x0, scale, W);
+  else stack_embed_kernel<false><<<T, 128, 0, st>>>(embed, tokens, x, x0, scale, W);
   return cudaGetLastError();
 }
 
@@ -246,6 +251,104 @@ cudaError_t launch_stack_final_norm(const float *x, const int *row_map, const fl
                                     cudaStream_t st) {
   if (f32) stack_final_norm_kernel<true><<<R, 256, 0, st>>>(x, row_map, g, out, W, eps);
   else stack_final_norm_kernel<false><<<R, 256, 0, st>>>(x, row_map, g, out, W, eps);
+  return cudaGetLastError();
+}
+
+// Layer-norm form of the boundary between two sublayers, one block per token, the row in shared memory.
+// y = bias + sum of the n_part slices of the product before; x += (y - mean(y)) / sqrt(var(y) + eps) * post_w + post_b;
+// cat (when given) receives [x ; x0] in the compute type (input of the projection in front of a loop pass);
+// h = (x - mean(x)) / sqrt(var(x) + eps) * pre_w + pre_b goes to hn (fp32, when given) and hc (compute type, when given).
+// The variance is the mean of the squared deviations from the mean (second pass over the row), all in fp32.
+template <bool F32>
+__global__ void __launch_bounds__(256) stack_boundary_ln_kernel(float *x, const float *y, int n_part, long long stride, const float *bias,
+                                                                const float *post_w, const float *post_b, const float *pre_w,
+                                                                const float *pre_b, float *hn, void *hc, const float *x0, void *cat,
+                                                                int W, float eps) {
+  extern __shared__ float row[];  // [W]
+  __shared__ float sh[32];
+  const long long t = blockIdx.x;
+  float *xr = x + t * W;
+  if (y) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = bias ? bias[i] : 0.f;
+      for (int k = 0; k < n_part; k++) v += y[(long long)k * stride + t * W + i];
+      row[i] = v;
+      s += v;
+    }
+    const float mean = block_sum(s, sh) / (float)W;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = row[i] - mean; q += dvi * dvi; }
+    const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = xr[i] + ((row[i] - mean) * r * post_w[i] + post_b[i]);
+      xr[i] = v;
+      row[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = xr[i];
+  }
+  if (cat) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      st_el<F32>(cat, t * 2 * W + i, row[i]);
+      st_el<F32>(cat, t * 2 * W + W + i, x0[t * W + i]);
+    }
+  }
+  if (!pre_w) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];  // each thread re-reads what it wrote itself
+  const float mean = block_sum(s, sh) / (float)W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = row[i] - mean; q += dvi * dvi; }
+  const float r = rsqrtf(block_sum(q, sh) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float h = (row[i] - mean) * r * pre_w[i] + pre_b[i];
+    if (hn) hn[t * W + i] = h;
+    if (hc) st_el<F32>(hc, t * W + i, h);
+  }
+}
+cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post_w,
+                                     const float *post_b, const float *pre_w, const float *pre_b, float *hn, void *hc, const float *x0,
+                                     void *cat, bool f32, int T, int W, float eps, cudaStream_t st) {
+  if ((size_t)W * 4 > 160 * 1024) return cudaErrorInvalidValue;
+  if (T <= 0) return cudaSuccess;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] {
+    cudaError_t e = cudaFuncSetAttribute(stack_boundary_ln_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_boundary_ln_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  }));
+  const size_t shb = (size_t)W * 4;
+  if (f32) stack_boundary_ln_kernel<true><<<T, 256, shb, st>>>(x, y, n_part, stride, bias, post_w, post_b, pre_w, pre_b, hn, hc, x0, cat, W, eps);
+  else stack_boundary_ln_kernel<false><<<T, 256, shb, st>>>(x, y, n_part, stride, bias, post_w, post_b, pre_w, pre_b, hn, hc, x0, cat, W, eps);
+  return cudaGetLastError();
+}
+
+template <bool F32>
+__global__ void stack_final_ln_kernel(const float *x, const int *row_map, const float *w, const float *b, void *out, int W, float eps) {
+  __shared__ float sh[32];
+  const long long r = blockIdx.x;
+  const float *xr = x + (long long)(row_map ? row_map[r] : r) * W;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += xr[i];
+  const float mean = block_sum(s, sh) / (float)W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = xr[i] - mean; q += dvi * dvi; }
+  const float k = rsqrtf(block_sum(q, sh) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, (xr[i] - mean) * k * w[i] + b[i]);
+}
+cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
+                                  float eps, cudaStream_t st) {
+  if (f32) stack_final_ln_kernel<true><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps);
+  else stack_final_ln_kernel<false><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps);
+  return cudaGetLastError();
+}
+
+__global__ void stack_scale_kernel(float *v, long long n, float s) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) v[i] *= s;
+}
+cudaError_t launch_stack_scale(float *v, long long n, float s, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  stack_scale_kernel<<<(int)std::min<long long>((n + 255) / 256, 148 * 8), 256, 0, st>>>(v, n, s);
   return cudaGetLastError();
 }
 
@@ -377,27 +480,41 @@ cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long
   return cudaGetLastError();
 }
 
-// ------------------------------------------------------------------------------------------------ clamped gated unit
-template <bool F32>
+// ------------------------------------------------------------------------------------------------ gated units
+__device__ __forceinline__ float gelu_tanh_(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <bool F32, int ACT>
 __global__ void stack_glu_kernel(const float *__restrict__ gu, const float *__restrict__ bias, void *__restrict__ act, const int *rows_ptr,
                                  int M, int ff, float limit) {
   const int rows = rows_ptr ? min(M, rows_ptr[0]) : M;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const float *gr = gu + (long long)r * 2 * ff;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
-      const float g = fminf(gr[c] + (bias ? bias[c] : 0.f), limit);
-      const float u = fminf(fmaxf(gr[ff + c] + (bias ? bias[ff + c] : 0.f), -limit), limit);
-      st_el<F32>(act, (long long)r * ff + c, g * sigmoid_precise(1.702f * g) * (u + 1.f));
+      float g = gr[c] + (bias ? bias[c] : 0.f), u = gr[ff + c] + (bias ? bias[ff + c] : 0.f);
+      float v;
+      if (ACT == DIS_ACT_GELU_TANH) v = gelu_tanh_(g) * u;
+      else {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        v = g * sigmoid_precise(1.702f * g) * (u + 1.f);
+      }
+      st_el<F32>(act, (long long)r * ff + c, v);
     }
   }
 }
 cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
-                             cudaStream_t st) {
+                             int kind, cudaStream_t st) {
   if (M <= 0) return cudaSuccess;
   // few rows: the columns are spread over grid.y as well
   const dim3 grid(std::min(M, 148 * 16), M >= 512 ? 1 : std::min((ff + 255) / 256, 16));
-  if (f32) stack_glu_kernel<true><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
-  else stack_glu_kernel<false><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+  if (kind == DIS_ACT_GELU_TANH) {
+    if (f32) stack_glu_kernel<true, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+    else stack_glu_kernel<false, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+  } else {
+    if (f32) stack_glu_kernel<true, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+    else stack_glu_kernel<false, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+  }
   return cudaGetLastError();
 }
 

@@ -56,42 +56,53 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
 }
 
 // The same recurrence with the state in registers: thread (warp w, lane l) owns S[w RI + ii][l + 32 jj], ii < RI, jj < RJ; q, k, v
-// of eight tokens at a time are staged in shared memory (SiLU applied) while the next eight are already on their way in
-// registers, so a group costs two barriers and no shared-memory traffic for the state.
+// of eight tokens at a time are staged in shared memory while the next eight are already on their way in registers, so a group
+// costs two barriers and no shared-memory traffic for the state.
+// GATE false: one decay per head, q, k, v through SiLU (lightning).  GATE true: gated linear attention -- the decay is a
+// vector per token and head, one factor per key channel (row of S), read from `dec` [T][H*d]; q is multiplied by qscale and
+// nothing goes through an activation.
 // MODE 0: a whole span, from the slot's state (zero at position 0) back into it.
 // Long spans are cut into segments of kLightSeg tokens that run side by side (grid x = span * max_seg + segment):
-// MODE 1: the segment's own contribution sum_s a^(n-1-s) k_s v_s^T to the state at its end (no outputs), into `seg`;
-// a carry kernel then walks the segments in order, S_in(c+1) = a^n S_in(c) + contribution(c), leaving S_in(c) in `seg`;
+// MODE 1: the segment's own contribution sum_s (prod_{u>s} a_u) k_s v_s^T to the state at its end (no outputs), into `seg`,
+// and with GATE the product of the segment's decays per channel into `seg_a`; a carry kernel then walks the segments in order,
+// S_in(c+1) = A_c S_in(c) + contribution(c), leaving S_in(c) in `seg`;
 // MODE 2: the segment's outputs, starting from S_in(c).
 constexpr int kLightTok = 8, kLightSeg = 64;
-template <int RI, int RJ, int MODE>
-__global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, const float *decay,
+struct LightCols { int q, k, v; };  // first column of head 0's q, k, v in a row of proj
+template <int RI, int RJ, int MODE, bool GATE>
+__global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, LightCols col,
+                                                                     const float *decay, const float *__restrict__ dec, float qscale,
                                                                      float *state, StackSpans sp, float *__restrict__ o, int H, int d,
-                                                                     int dv, float *seg, int max_seg) {
+                                                                     int dv, float *seg, float *seg_a, int max_seg) {
   extern __shared__ __align__(16) float shm[];
-  constexpr int DP = RI * 8, DVP = RJ * 32, LD = kLightTok * (2 * DP + DVP) / 256;
+  constexpr int DP = RI * 8, DVP = RJ * 32, LD = kLightTok * ((GATE ? 3 : 2) * DP + DVP) / 256;
   // heads vary fastest over the grid: the CTAs that run at the same time then read whole rows of the projections rather than
   // one head's columns at a stride of a row, which would keep most memory channels idle
   const int h = blockIdx.x % H, sc = blockIdx.x / H;
   const int s = MODE == 0 ? sc : sc / max_seg;
   const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
   int first = tok0, n = len;
-  float *sg = nullptr;
+  float *sg = nullptr, *sga = nullptr;
   if (MODE != 0) {
     const int c = sc - s * max_seg;
     if (c * kLightSeg >= len) return;
     first = tok0 + c * kLightSeg;
     n = min(kLightSeg, len - c * kLightSeg);
     sg = seg + ((size_t)(tok0 / kLightSeg + s + c) * H + h) * d * dv;
+    if (GATE) sga = seg_a + ((size_t)(tok0 / kLightSeg + s + c) * H + h) * d;
   }
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, i0 = w * RI;
   float *qs = shm;                             // [tok][DP]
   float *ks = qs + kLightTok * DP;             // [tok][DP]
   float *vs = ks + kLightTok * DP;             // [tok][DVP]
   float *part = vs + kLightTok * DVP;          // [tok][8][DVP]
+  float *as = part + kLightTok * 8 * DVP;      // [tok][DP] (GATE)
   float *st = state + ((long long)slot * H + h) * d * dv;
-  const float a = decay[h];
+  const float a = GATE ? 1.f : decay[h];
   float S[RI][RJ];
+  float A[GATE ? RI : 1];  // MODE 1: running product of the decays of this thread's rows
+#pragma unroll
+  for (int ii = 0; ii < (GATE ? RI : 1); ii++) A[ii] = 1.f;
 #pragma unroll
   for (int ii = 0; ii < RI; ii++)
 #pragma unroll
@@ -104,7 +115,7 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       }
       S[ii][jj] = v;
     }
-  const int per = 2 * d + dv;
+  const int per = (GATE ? 3 : 2) * d + dv;
   float tmp[LD];
   auto fetch = [&](int t0) {
     const int ct = min(kLightTok, n - t0);
@@ -113,9 +124,10 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       const int e = threadIdx.x + u * 256, t = e / per, c = e - t * per;
       if (t < ct) {
         const float *row = proj + (long long)(first + t0 + t) * ld;
-        const long long col = c < d ? (long long)h * d + c : c < 2 * d ? (long long)H * d + (long long)h * d + (c - d)
-                                                                        : (long long)2 * H * d + (long long)h * dv + (c - 2 * d);
-        tmp[u] = row[col];
+        if (c < d) tmp[u] = row[col.q + (long long)h * d + c];
+        else if (c < 2 * d) tmp[u] = row[col.k + (long long)h * d + (c - d)];
+        else if (c < 2 * d + dv) tmp[u] = row[col.v + (long long)h * dv + (c - 2 * d)];
+        else tmp[u] = dec[(long long)(first + t0 + t) * H * d + (long long)h * d + (c - 2 * d - dv)];
       }
     }
   };
@@ -127,8 +139,10 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
     for (int u = 0; u < LD; u++) {
       const int e = threadIdx.x + u * 256, t = e / per, c = e - t * per;
       if (t < ct) {
-        float *dst = c < d ? qs + t * DP + c : c < 2 * d ? ks + t * DP + (c - d) : vs + t * DVP + (c - 2 * d);
-        *dst = silu_(tmp[u]);
+        if (c < d) qs[t * DP + c] = GATE ? tmp[u] * qscale : silu_(tmp[u]);
+        else if (c < 2 * d) ks[t * DP + (c - d)] = GATE ? tmp[u] : silu_(tmp[u]);
+        else if (c < 2 * d + dv) vs[t * DVP + (c - 2 * d)] = GATE ? tmp[u] : silu_(tmp[u]);
+        else as[t * DP + (c - 2 * d - dv)] = tmp[u];
       }
     }
     if (t0 + kLightTok < n) fetch(t0 + kLightTok);
@@ -141,13 +155,16 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       for (int i4 = 0; i4 < RI; i4 += 4) {
         const float4 k4 = *reinterpret_cast<const float4 *>(ks + t * DP + i0 + i4);
         const float4 q4 = *reinterpret_cast<const float4 *>(qs + t * DP + i0 + i4);
-        const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+        float4 a4 = make_float4(a, a, a, a);
+        if (GATE) a4 = *reinterpret_cast<const float4 *>(as + t * DP + i0 + i4);
+        const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w}, av[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
         for (int u = 0; u < 4; u++) {
           if (i0 + i4 + u < d) {
+            if (GATE && MODE == 1) A[GATE ? i4 + u : 0] *= av[u];
 #pragma unroll
             for (int jj = 0; jj < RJ; jj++) {
-              S[i4 + u][jj] = fmaf(a, S[i4 + u][jj], kv[u] * vj[jj]);
+              S[i4 + u][jj] = fmaf(av[u], S[i4 + u][jj], kv[u] * vj[jj]);
               if (MODE != 1) acc[jj] = fmaf(S[i4 + u][jj], qv[u], acc[jj]);
             }
           }
@@ -178,36 +195,49 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       const int i = i0 + ii, j = l + jj * 32;
       if (i < d && j < dv) dst[(size_t)i * dv + j] = S[ii][jj];
     }
+  if (GATE && MODE == 1 && l == 0) {
+#pragma unroll
+    for (int ii = 0; ii < RI; ii++)
+      if (i0 + ii < d) sga[i0 + ii] = A[GATE ? ii : 0];
+  }
 }
 
 // Segment carry: one thread per state element walks the span's segments in order.  Elements vary fastest over the grid, then
-// heads, so that the CTAs that run at the same time walk one contiguous stretch of every segment.
-__global__ void stack_lightning_carry_kernel(const float *decay, float *state, StackSpans sp, float *seg, int H, int n_el) {
+// heads, so that the CTAs that run at the same time walk one contiguous stretch of every segment.  seg_a (gated form): the
+// product of each segment's decays per key channel; otherwise the head's decay to the power of the segment's length.
+__global__ void stack_lightning_carry_kernel(const float *decay, const float *seg_a, float *state, StackSpans sp, float *seg, int H,
+                                             int d, int dv) {
+  const int n_el = d * dv;
   const int nz = (n_el + blockDim.x - 1) / blockDim.x;
   const int z = blockIdx.x % nz, h = (blockIdx.x / nz) % H, s = blockIdx.x / (nz * H);
   const int e = z * blockDim.x + threadIdx.x;
   if (e >= n_el) return;
   const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
   float *st = state + ((long long)slot * H + h) * n_el;
-  const float a = decay[h];
+  const float a = seg_a ? 1.f : decay[h];
   float S = pos0 > 0 ? st[e] : 0.f;
   float a64 = 1.f;
   for (int k = 0; k < kLightSeg; k++) a64 *= a;
   const int nseg = (len + kLightSeg - 1) / kLightSeg;
   float *sg0 = seg + ((size_t)(tok0 / kLightSeg + s) * H + h) * n_el + e;
-  const size_t step = (size_t)H * n_el;
+  const float *sa0 = seg_a ? seg_a + ((size_t)(tok0 / kLightSeg + s) * H + h) * d + e / dv : nullptr;
+  const size_t step = (size_t)H * n_el, step_a = (size_t)H * d;
   constexpr int U = 8;  // segments whose contributions are fetched together, ahead of the chain that joins them
   for (int c0 = 0; c0 < nseg; c0 += U) {
-    float own[U];
+    float own[U], fa[U];
 #pragma unroll
-    for (int u = 0; u < U; u++) own[u] = c0 + u < nseg ? sg0[(size_t)(c0 + u) * step] : 0.f;
+    for (int u = 0; u < U; u++) {
+      own[u] = c0 + u < nseg ? sg0[(size_t)(c0 + u) * step] : 0.f;
+      fa[u] = (sa0 && c0 + u < nseg) ? sa0[(size_t)(c0 + u) * step_a] : 1.f;
+    }
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int c = c0 + u;
       if (c < nseg) {
         const int n = min(kLightSeg, len - c * kLightSeg);
         float an = a64;
-        if (n < kLightSeg) {
+        if (sa0) an = fa[u];
+        else if (n < kLightSeg) {
           an = 1.f;
           for (int k = 0; k < n; k++) an *= a;
         }
@@ -223,38 +253,107 @@ int stack_lightning_seg_tokens() { return kLightSeg; }
 size_t stack_lightning_seg_floats(int cap_tokens, int max_spans, int H, int d, int dv) {
   return (size_t)(cap_tokens / kLightSeg + max_spans + 1) * H * d * dv;
 }
+size_t stack_lightning_seg_decay_floats(int cap_tokens, int max_spans, int H, int d) {
+  return (size_t)(cap_tokens / kLightSeg + max_spans + 1) * H * d;
+}
 
-template <int RI, int RJ>
-static cudaError_t lightning_reg(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp, float *o,
-                                 int H, int d, int dv, float *seg, int max_len, cudaStream_t st) {
-  const size_t sh = (size_t)kLightTok * (2 * RI * 8 + RJ * 32 + 8 * RJ * 32) * sizeof(float);
+template <int RI, int RJ, bool GATE>
+static cudaError_t lightning_reg(const float *proj, long long ld, LightCols col, const float *decay, const float *dec, float qscale,
+                                 float *state, const StackSpans &sp, float *o, int H, int d, int dv, float *seg, float *seg_a,
+                                 int max_len, cudaStream_t st) {
+  const size_t sh = (size_t)kLightTok * ((GATE ? 3 : 2) * RI * 8 + RJ * 32 + 8 * RJ * 32) * sizeof(float);
   static DeviceOnce once;
   DIS_CUDA_TRY(once.run([&] {
-    cudaError_t e = cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 0, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 1, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_lightning_reg_kernel<RI, RJ, 2, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
   }));
-  if (!seg || max_len <= kLightSeg) {
-    stack_lightning_reg_kernel<RI, RJ, 0><<<sp.n_spans * H, 256, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv, nullptr, 1);
+  if (!seg || (GATE && !seg_a) || max_len <= kLightSeg) {
+    stack_lightning_reg_kernel<RI, RJ, 0, GATE><<<sp.n_spans * H, 256, sh, st>>>(proj, ld, col, decay, dec, qscale, state, sp, o, H, d, dv, nullptr, nullptr, 1);
     return cudaGetLastError();
   }
   const int max_seg = (max_len + kLightSeg - 1) / kLightSeg;
-  stack_lightning_reg_kernel<RI, RJ, 1><<<sp.n_spans * max_seg * H, 256, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_seg);
-  stack_lightning_carry_kernel<<<sp.n_spans * H * ((d * dv + 255) / 256), 256, 0, st>>>(decay, state, sp, seg, H, d * dv);
-  stack_lightning_reg_kernel<RI, RJ, 2><<<sp.n_spans * max_seg * H, 256, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_seg);
+  stack_lightning_reg_kernel<RI, RJ, 1, GATE><<<sp.n_spans * max_seg * H, 256, sh, st>>>(proj, ld, col, decay, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_seg);
+  stack_lightning_carry_kernel<<<sp.n_spans * H * ((d * dv + 255) / 256), 256, 0, st>>>(decay, GATE ? seg_a : nullptr, state, sp, seg, H, d, dv);
+  stack_lightning_reg_kernel<RI, RJ, 2, GATE><<<sp.n_spans * max_seg * H, 256, sh, st>>>(proj, ld, col, decay, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_seg);
   return cudaGetLastError();
 }
 
 cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
                                    float *o, int H, int d, int dv, float *seg, int max_len, cudaStream_t st) {
   const int threads = 256;
-  if (d <= 64 && dv <= 64) return lightning_reg<8, 2>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_len, st);
-  if (d <= 128 && dv <= 128) return lightning_reg<16, 4>(proj, ld, decay, state, sp, o, H, d, dv, seg, max_len, st);
+  const LightCols col{0, H * d, 2 * H * d};
+  if (d <= 64 && dv <= 64) return lightning_reg<8, 2, false>(proj, ld, col, decay, nullptr, 1.f, state, sp, o, H, d, dv, seg, nullptr, max_len, st);
+  if (d <= 128 && dv <= 128) return lightning_reg<16, 4, false>(proj, ld, col, decay, nullptr, 1.f, state, sp, o, H, d, dv, seg, nullptr, max_len, st);
   const size_t sh = ((size_t)d * dv + 2 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
   static DeviceOnce once;
   DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
   stack_lightning_kernel<<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ gated linear attention
+// Decays: z[c] = b[c] + sum_r A2[c][r] u[r] with u the rank-sized bottleneck (columns a_off .. of proj, fp32), then
+// a[c] = sigmoid(z[c])^(1/tau) = exp(-softplus(-z[c]) / tau), everything fp32.  One block per token.
+template <bool WF32>
+__global__ void __launch_bounds__(128) stack_gla_decay_kernel(const float *proj, long long ld, int a_off, const void *a2, const float *b,
+                                                              int n, int rank, float inv_tau, float *dec) {
+  extern __shared__ float u[];  // [rank]
+  const long long t = blockIdx.x;
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) u[r] = proj[t * ld + a_off + r];
+  __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float z = b[c];
+    for (int r = 0; r < rank; r++) z = fmaf(ld_el<WF32>(a2, (long long)c * rank + r), u[r], z);
+    // -log sigmoid(z) = softplus(-z) = max(-z, 0) + log1p(exp(-|z|))
+    const float sp = fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)));
+    dec[t * n + c] = expf(-sp * inv_tau);
+  }
+}
+cudaError_t launch_stack_gla_decay(const float *proj, long long ld, int a_off, const void *a2, bool w_f32, const float *b, int T, int n,
+                                   int rank, float tau, float *dec, cudaStream_t st) {
+  if (T <= 0) return cudaSuccess;
+  if (w_f32) stack_gla_decay_kernel<true><<<T, 128, (size_t)rank * 4, st>>>(proj, ld, a_off, a2, b, n, rank, 1.f / tau, dec);
+  else stack_gla_decay_kernel<false><<<T, 128, (size_t)rank * 4, st>>>(proj, ld, a_off, a2, b, n, rank, 1.f / tau, dec);
+  return cudaGetLastError();
+}
+
+// The recurrence itself: the register kernel above in its gated form (dim, vdim <= 128).
+cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *dec, float *state,
+                             const StackSpans &sp, float *o, int H, int d, int dv, float *seg, float *seg_a, int max_len,
+                             cudaStream_t st) {
+  const LightCols col{q_off, k_off, v_off};
+  const float qscale = 1.f / sqrtf((float)d);
+  if (d <= 64 && dv <= 64) return lightning_reg<8, 2, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 128 && dv <= 128) return lightning_reg<16, 4, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  return cudaErrorInvalidValue;
+}
+
+// out[t][off + h*dv + j] = scale * o[t][h][j] / rms(o[t][h]) * w[j] * silu(gate[t][h*dv + j]): the norm runs over one head's dv
+// outputs, its gain vector is shared by the heads.  One warp per (token, head).
+template <bool F32>
+__global__ void __launch_bounds__(256) stack_headnorm_silu_kernel(const float *o, const float *w, const float *gate, long long ldg, void *out,
+                                                                  long long ldo, int off, float scale, int rows, int H, int dv, float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int t = row / H, h = row - t * H;
+  const float *r = o + (long long)row * dv;
+  float s = 0.f;
+  for (int j = l; j < dv; j += 32) s += r[j] * r[j];
+  s = warp_sum(s);
+  const float k = rsqrtf(s / (float)dv + eps) * scale;
+  for (int j = l; j < dv; j += 32) {
+    const float g = gate[(long long)t * ldg + (long long)h * dv + j];
+    st_el<F32>(out, (long long)t * ldo + off + (long long)h * dv + j, r[j] * k * w[j] * silu_(g));
+  }
+}
+cudaError_t launch_stack_headnorm_silu(const float *o, const float *w, const float *gate, long long ldg, void *out, long long ldo,
+                                       int off, float scale, bool f32, int T, int H, int dv, float eps, cudaStream_t st) {
+  const int rows = T * H;
+  if (rows <= 0) return cudaSuccess;
+  if (f32) stack_headnorm_silu_kernel<true><<<(rows + 7) / 8, 256, 0, st>>>(o, w, gate, ldg, out, ldo, off, scale, rows, H, dv, eps);
+  else stack_headnorm_silu_kernel<false><<<(rows + 7) / 8, 256, 0, st>>>(o, w, gate, ldg, out, ldo, off, scale, rows, H, dv, eps);
   return cudaGetLastError();
 }
 

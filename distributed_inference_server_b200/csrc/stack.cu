@@ -61,6 +61,7 @@ cudaError_t Engine::stack_meta(StepMeta &s, int cap_t, int cap_rows) {
   s.o_rowmap = sec(cr * 4); s.o_temp = sec(cr * 4); s.o_topp = sec(cr * 4); s.o_seed = sec(cr * 8); s.o_step = sec(cr * 8);
   s.o_qb_tok0 = sec(ct * 4); s.o_qb_len = sec(ct * 4); s.o_qb_pos0 = sec(ct * 4); s.o_qb_ptrow = sec(ct * 4);
   s.o_ab_tok0 = sec(ct * 4); s.o_ab_len = sec(ct * 4);
+  s.o_kb_tok0 = sec(ct * 4); s.o_kb_len = sec(ct * 4);
   s.o_arstep = sec(16);
   s.bytes = o;
   cudaError_t e = cudaMallocHost(reinterpret_cast<void **>(&s.host), s.bytes);
@@ -124,8 +125,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         const dis_layer_config &src = M.layers[(size_t)lc.kv_from].c;
         if (src.mixer != DIS_MIX_LATENT || src.kv_from >= 0 || src.kv_rank != lc.kv_rank || src.rot_dim != lc.rot_dim)
           return fail(DIS_ERR_INVALID_ARGUMENT, at + "kv_from must name a latent layer with a cache of its own and the same kv_rank and rot_dim");
-        L.kv_layer = lc.kv_from;
-      } else L.kv_layer = i;
+      }
       L.q_off = 0;
       L.dkv_off = lc.heads * (lc.dim + lc.rot_dim);
       L.g_off = L.dkv_off + (lc.kv_from < 0 ? lc.kv_rank + lc.rot_dim : 0);
@@ -139,12 +139,63 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         stack_bq = std::min(stack_bq, std::max(1, 16 / lc.heads));
         stack_lat_mma = true;
       }
+    } else if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) {
+      if (lc.heads <= 0 || lc.kv_heads <= 0 || lc.heads % lc.kv_heads || lc.dim <= 0 || lc.vdim <= 0 || lc.rot_dims < 0 || lc.rot_dims > lc.dim || (lc.rot_dims & 1))
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "attention needs heads (a multiple of kv_heads), dim, vdim and an even rot_dims <= dim");
+      if ((lc.attn_flags & DIS_ATTN_V_IS_K) && lc.vdim != lc.dim) return fail(DIS_ERR_INVALID_ARGUMENT, at + "values that are the keys need vdim == dim");
+      if ((lc.attn_flags & DIS_ATTN_ROT_V) && (lc.vdim & 1)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "rotated values need an even vdim");
+      if (lc.rot_factor != 0.f && (lc.rot_high == lc.rot_low || lc.rot_original <= 0 || lc.rot_low <= 0.f || lc.rot_high <= 0.f))
+        return fail(DIS_ERR_INVALID_ARGUMENT, at + "rotary scaling needs original > 0 and 0 < low != high");
+      const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
+      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, sc->norm_eps};
+      const int bq = stack_attn_block_tokens(sa);
+      if (((size_t)32 * (d + dv + 10) + (size_t)(H / G) * (d + dv + 2)) * 4 > 200 * 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "dim + vdim does not fit shared memory");
+      stack_abq = stack_abq ? std::min(stack_abq, bq) : bq;
+      stack_att_heads = std::max(stack_att_heads, H);
+      stack_att_groups = stack_att_groups ? std::min(stack_att_groups, G) : G;
+      stack_att_rec = std::max(stack_att_rec, (size_t)H * (dv + 2));
+      L.q_off = 0; L.k_off = H * d; L.v_off = L.k_off + G * d;
+      L.n_in = L.v_off + ((lc.attn_flags & DIS_ATTN_V_IS_K) ? 0 : G * dv);
+      L.n_act = H * dv;
+      if (lc.mixer == DIS_MIX_PARALLEL) {
+        const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim;
+        if (Hr <= 0 || dr <= 0 || dvr <= 0 || lc.gla_rank <= 0 || !(lc.gla_tau > 0.f)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "gated linear attention needs heads, dim, vdim, rank and tau > 0");
+        if (dr > 128 || dvr > 128) return fail(DIS_ERR_INVALID_ARGUMENT, at + "gated linear attention: dim and vdim up to 128");
+        L.gq_off = L.n_in; L.gk_off = L.gq_off + Hr * dr; L.gv_off = L.gk_off + Hr * dr; L.gg_off = L.gv_off + Hr * dvr;
+        L.ga_off = L.gg_off + Hr * dvr;
+        L.n_in = L.ga_off + lc.gla_rank;
+        L.n_act += Hr * dvr;
+      }
     } else return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown mixer");
+    if (lc.mlp_act != DIS_ACT_CLAMPED && lc.mlp_act != DIS_ACT_GELU_TANH) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward activation");
     if (lc.mlp == DIS_MLP_DENSE) { if (lc.ff <= 0) return fail(DIS_ERR_INVALID_ARGUMENT, at + "ff"); }
     else if (lc.mlp == DIS_MLP_MOE) {
       if (lc.ff <= 0 || lc.experts <= 0 || lc.top <= 0 || lc.top > lc.experts || lc.top > 32 || lc.experts > 1024)
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "experts: 1 <= top <= min(experts, 32), experts <= 1024");
     } else if (lc.mlp != DIS_MLP_NONE) return fail(DIS_ERR_INVALID_ARGUMENT, at + "unknown feed-forward kind");
+  }
+  if (sc->norm_kind != DIS_NORM_RMS_SCALAR && sc->norm_kind != DIS_NORM_LAYER) return fail(DIS_ERR_INVALID_ARGUMENT, "stack: norm_kind");
+  if (sc->loop_times < 0 || (sc->loop_times > 0 && !(0 <= sc->loop_start && sc->loop_start < sc->loop_stop && sc->loop_stop <= sc->n_layers)))
+    return fail(DIS_ERR_INVALID_ARGUMENT, "stack: a loop needs 0 <= loop_start < loop_stop <= n_layers");
+  if (M.c.embed_scale == 0.f) M.c.embed_scale = 1.f;
+  if (M.c.logit_scale == 0.f) M.c.logit_scale = 1.f;
+  // ---- the layer runs of one pass: the looped stretch once per loop pass
+  for (int i = 0; i < sc->n_layers; i++) {
+    if (sc->loop_times > 0 && i == sc->loop_start) {
+      for (int t = 0; t < sc->loop_times; t++)
+        for (int j = sc->loop_start; j < sc->loop_stop; j++) { StackRun r; r.layer = j; r.loop_pass = j == sc->loop_start ? t : -1; M.runs.push_back(r); }
+      i = sc->loop_stop - 1;
+      continue;
+    }
+    StackRun r; r.layer = i;
+    M.runs.push_back(r);
+  }
+  for (size_t ri = 0; ri < M.runs.size(); ri++) {  // a latent layer that borrows a cache reads the latest run of its owner
+    const StackLayer &L = M.layers[(size_t)M.runs[ri].layer];
+    if (L.c.mixer != DIS_MIX_LATENT) continue;
+    M.runs[ri].kv_run = (int)ri;
+    if (L.c.kv_from >= 0)
+      for (size_t rj = 0; rj < ri; rj++) if (M.runs[rj].layer == L.c.kv_from) M.runs[ri].kv_run = (int)rj;
   }
 
   int ndev = 0;
@@ -182,9 +233,22 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   name("embed", &M.embed, 0, {sc->vocab, W}, -1);
   name("head", &M.head, 0, {sc->vocab, W}, -1);
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.final_g), 4));
+  const bool ln = sc->norm_kind == DIS_NORM_LAYER;
+  if (ln) {
+    ENG_CUDA(tensor(M.final_w, (size_t)W, true));
+    ENG_CUDA(tensor(M.final_b, (size_t)W, true));
+    name("final.norm", &M.final_w, 0, {W}, -1);
+    name("final.norm.b", &M.final_b, 0, {W}, -1);
+  }
+  if (sc->loop_times > 0) {
+    ENG_CUDA(tensor(M.loop_in, (size_t)W * 2 * W, M.f32));
+    ENG_CUDA(tensor(M.loop_step, (size_t)sc->loop_times * W, true));
+    name("loop.in", &M.loop_in, 0, {W, 2 * W}, -1);
+    name("loop.step", &M.loop_step, 0, {sc->loop_times, W}, -1);
+  }
   static StackTensor dummy;  // scalars are written through their own small tensors below
   (void)dummy;
-  size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1;
+  size_t max_proj = 1, max_mix = 1, max_act = 1, max_qf = 1, max_vrot = 0, max_dec = 0;
   int max_top = 0, max_e = 0;
   const size_t slots = (size_t)max_batch;
   std::vector<StackTensor *> scalars;
@@ -195,10 +259,16 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     ENG_CUDA(alloc(reinterpret_cast<void **>(&L.g4), 16));
     if (taps >= 1) {
       ENG_CUDA(alloc(reinterpret_cast<void **>(&L.canon1), (size_t)W * taps * 4));
-      if (taps > 1) ENG_CUDA(alloc(reinterpret_cast<void **>(&L.cstate1), slots * (taps - 1) * W * 4));
-      if (lc.mlp != DIS_MLP_NONE) {
-        ENG_CUDA(alloc(reinterpret_cast<void **>(&L.canon2), (size_t)W * taps * 4));
-        if (taps > 1) ENG_CUDA(alloc(reinterpret_cast<void **>(&L.cstate2), slots * (taps - 1) * W * 4));
+      if (lc.mlp != DIS_MLP_NONE) ENG_CUDA(alloc(reinterpret_cast<void **>(&L.canon2), (size_t)W * taps * 4));
+    }
+    if (ln) {
+      const char *gn[4] = {"norm1", "norm1b", "norm2", "norm2b"};
+      for (int k = 0; k < 4; k++) {
+        if (k >= 2 && lc.mlp == DIS_MLP_NONE) continue;
+        ENG_CUDA(tensor(L.ln_w[k], (size_t)W, true));
+        ENG_CUDA(tensor(L.ln_b[k], (size_t)W, true));
+        name(pre + gn[k], &L.ln_w[k], 0, {W}, i);
+        name(pre + gn[k] + ".b", &L.ln_b[k], 0, {W}, i);
       }
     }
     ENG_CUDA(tensor(L.w_in, (size_t)L.n_in * W, M.f32));
@@ -215,9 +285,81 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       name(pre + "mix.norm", &L.norm_w, 0, {H * dv}, i);
       ENG_CUDA(tensor(L.decay_d, (size_t)H, true));
       ENG_CUDA(cudaMemcpy(L.decay_d.ptr, L.decay.data(), (size_t)H * 4, cudaMemcpyHostToDevice));
-      ENG_CUDA(alloc(reinterpret_cast<void **>(&L.state), slots * H * d * dv * 4));
       max_mix = std::max(max_mix, (size_t)H * dv);
       max_act = std::max(max_act, (size_t)H * dv);
+    } else if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) {
+      const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
+      const std::string a = pre + (lc.mixer == DIS_MIX_PARALLEL ? "mix.left." : "mix.");
+      name(a + "q", &L.w_in, 0, {H * d, W}, i);
+      name(a + "k", &L.w_in, (size_t)L.k_off * W, {G * d, W}, i);
+      if (!(lc.attn_flags & DIS_ATTN_V_IS_K)) name(a + "v", &L.w_in, (size_t)L.v_off * W, {G * dv, W}, i);
+      ENG_CUDA(tensor(L.w_o, (size_t)W * L.n_act, M.f32));
+      {
+        name(a + "o", &L.w_o, 0, {W, H * dv}, i, 2);
+        stack_names[a + "o"].ld = L.n_act;
+      }
+      if (lc.attn_flags & DIS_ATTN_BIAS) {
+        ENG_CUDA(tensor(L.b_in, (size_t)L.n_in, true));
+        name(a + "q.b", &L.b_in, 0, {H * d}, i);
+        name(a + "k.b", &L.b_in, (size_t)L.k_off, {G * d}, i);
+        ENG_CUDA(tensor(L.b_o, (size_t)W, true));
+        name(a + "o.b", &L.b_o, 0, {W}, i);
+      }
+      if (lc.attn_flags & DIS_ATTN_QK_NORM) {
+        ENG_CUDA(tensor(L.qk_norm, (size_t)(H + G) * d, true));
+        name(a + "q.norm", &L.qk_norm, 0, {H * d}, i);
+        name(a + "k.norm", &L.qk_norm, (size_t)H * d, {G * d}, i);
+      }
+      if (lc.attn_flags & DIS_ATTN_SIGMOID) {
+        ENG_CUDA(tensor(L.temp_pb, (size_t)2 * H, true));
+        name(a + "temp", &L.temp_pb, 0, {H}, i);
+        name(a + "pb", &L.temp_pb, (size_t)H, {H}, i);
+      }
+      {  // frequency tables, formed in double: f_i = base^(-2i/n), rescaled by wavelength where the configuration asks
+        std::vector<double> f((size_t)lc.rot_dims / 2 + 1), fv((size_t)dv / 2 + 1);
+        const double kPi = 3.14159265358979323846;
+        for (int k = 0; k < lc.rot_dims / 2; k++) {
+          double v = std::pow((double)lc.rot_base, -2.0 * k / (double)lc.rot_dims);
+          if (lc.rot_factor != 0.f) {
+            const double wl = 2.0 * kPi / v, orig = (double)lc.rot_original;
+            if (wl > orig / (double)lc.rot_low) v = v / (double)lc.rot_factor;
+            else if (!(wl < orig / (double)lc.rot_high)) {
+              const double sm = (orig / wl - (double)lc.rot_low) / ((double)lc.rot_high - (double)lc.rot_low);
+              v = (1.0 - sm) * v / (double)lc.rot_factor + sm * v;
+            }
+          }
+          f[(size_t)k] = v;
+        }
+        for (int k = 0; k < dv / 2; k++) fv[(size_t)k] = std::pow((double)lc.rot_base, -2.0 * k / (double)dv);
+        ENG_CUDA(alloc(reinterpret_cast<void **>(&L.freq), f.size() * 8));
+        ENG_CUDA(cudaMemcpy(L.freq, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
+        if (lc.attn_flags & DIS_ATTN_ROT_V) {
+          ENG_CUDA(alloc(reinterpret_cast<void **>(&L.vfreq), fv.size() * 8));
+          ENG_CUDA(cudaMemcpy(L.vfreq, fv.data(), fv.size() * 8, cudaMemcpyHostToDevice));
+          max_vrot = std::max(max_vrot, (size_t)dv);
+        }
+      }
+      max_qf = std::max(max_qf, (size_t)H * d);
+      if (lc.mixer == DIS_MIX_PARALLEL) {
+        const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim, rk = lc.gla_rank;
+        const std::string r = pre + "mix.right.";
+        name(r + "q", &L.w_in, (size_t)L.gq_off * W, {Hr * dr, W}, i);
+        name(r + "k", &L.w_in, (size_t)L.gk_off * W, {Hr * dr, W}, i);
+        name(r + "v", &L.w_in, (size_t)L.gv_off * W, {Hr * dvr, W}, i);
+        name(r + "g", &L.w_in, (size_t)L.gg_off * W, {Hr * dvr, W}, i);
+        name(r + "a1", &L.w_in, (size_t)L.ga_off * W, {rk, W}, i);
+        name(r + "o", &L.w_o, (size_t)H * dv, {W, Hr * dvr}, i, 2);
+        stack_names[r + "o"].ld = L.n_act;
+        ENG_CUDA(tensor(L.a2, (size_t)Hr * dr * rk, M.f32));
+        name(r + "a2", &L.a2, 0, {Hr * dr, rk}, i);
+        ENG_CUDA(tensor(L.a2_b, (size_t)Hr * dr, true));
+        name(r + "a2.b", &L.a2_b, 0, {Hr * dr}, i);
+        ENG_CUDA(tensor(L.gla_norm, (size_t)dvr, true));
+        name(r + "norm", &L.gla_norm, 0, {dvr}, i);
+        max_mix = std::max(max_mix, (size_t)Hr * dvr);
+        max_dec = std::max(max_dec, (size_t)Hr * dr);
+      }
+      max_act = std::max(max_act, (size_t)L.n_act);
     } else if (lc.mixer == DIS_MIX_MINGRU) {
       const int n = lc.width;
       name(pre + "mix.z", &L.w_in, 0, {n, W}, i);
@@ -228,7 +370,6 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       name(pre + "mix.x.b", &L.b_in, (size_t)n, {n}, i);
       ENG_CUDA(tensor(L.w_o, (size_t)W * n, M.f32));
       name(pre + "mix.o", &L.w_o, 0, {W, n}, i);
-      ENG_CUDA(alloc(reinterpret_cast<void **>(&L.state), slots * n * 4));
       max_act = std::max(max_act, (size_t)n);
     } else {
       const int H = lc.heads, d = lc.dim, dr = lc.rot_dim, dv = lc.vdim, r = lc.kv_rank;
@@ -256,15 +397,17 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     if (lc.mlp == DIS_MLP_DENSE) {
       const int ff = lc.ff;
       ENG_CUDA(tensor(L.w_gu, (size_t)2 * ff * W, M.f32));
-      ENG_CUDA(tensor(L.b_gu, (size_t)2 * ff, true));
       ENG_CUDA(tensor(L.w_down, (size_t)W * ff, M.f32));
-      ENG_CUDA(tensor(L.b_down, (size_t)W, true));
       name(pre + "mlp.gate", &L.w_gu, 0, {ff, W}, i);
       name(pre + "mlp.up", &L.w_gu, (size_t)ff * W, {ff, W}, i);
-      name(pre + "mlp.gate.b", &L.b_gu, 0, {ff}, i);
-      name(pre + "mlp.up.b", &L.b_gu, (size_t)ff, {ff}, i);
       name(pre + "mlp.down", &L.w_down, 0, {W, ff}, i);
-      name(pre + "mlp.down.b", &L.b_down, 0, {W}, i);
+      if (lc.mlp_act == DIS_ACT_CLAMPED) {  // the clamped unit carries biases, the gelu unit none
+        ENG_CUDA(tensor(L.b_gu, (size_t)2 * ff, true));
+        ENG_CUDA(tensor(L.b_down, (size_t)W, true));
+        name(pre + "mlp.gate.b", &L.b_gu, 0, {ff}, i);
+        name(pre + "mlp.up.b", &L.b_gu, (size_t)ff, {ff}, i);
+        name(pre + "mlp.down.b", &L.b_down, 0, {W}, i);
+      }
       max_proj = std::max(max_proj, (size_t)2 * ff);
       max_act = std::max(max_act, (size_t)ff);
     } else if (lc.mlp == DIS_MLP_MOE) {
@@ -291,7 +434,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     StackLayer &L = M.layers[(size_t)i];
     const std::string pre = "l" + std::to_string(i) + ".";
     const char *gn[4] = {"norm1", "norm1b", "norm2", "norm2b"};
-    for (int k = 0; k < 4; k++) {
+    for (int k = 0; k < 4 && !ln; k++) {
       if (k >= 2 && L.c.mlp == DIS_MLP_NONE) continue;
       StackTensor *v = new StackTensor();
       v->ptr = L.g4 + k; v->n = 1; v->f32 = true;
@@ -311,11 +454,22 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       }
     }
   }
-  {
+  if (!ln) {
     StackTensor *v = new StackTensor();
     v->ptr = M.final_g; v->n = 1; v->f32 = true;
     scalars.push_back(v);
     name("final.norm", v, 0, {}, -1);
+  }
+  // ---- recurrent state of every layer run (one slot per sequence)
+  for (StackRun &R : M.runs) {
+    const dis_layer_config &lc = M.layers[(size_t)R.layer].c;
+    if (taps > 1) {
+      ENG_CUDA(alloc(reinterpret_cast<void **>(&R.cstate1), slots * (taps - 1) * W * 4));
+      if (lc.mlp != DIS_MLP_NONE) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.cstate2), slots * (taps - 1) * W * 4));
+    }
+    if (lc.mixer == DIS_MIX_LIGHTNING) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.heads * lc.dim * lc.vdim * 4));
+    else if (lc.mixer == DIS_MIX_MINGRU) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.width * 4));
+    else if (lc.mixer == DIS_MIX_PARALLEL) ENG_CUDA(alloc(reinterpret_cast<void **>(&R.state), slots * lc.gla_heads * lc.gla_dim * lc.gla_vdim * 4));
   }
   M.views.assign(scalars.begin(), scalars.end());
   // ---- activations
@@ -330,6 +484,16 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   ENG_CUDA(alloc(reinterpret_cast<void **>(&M.qf), cap * max_qf * 4));
   ENG_CUDA(alloc(&M.act, cap * max_act * esz));
   ENG_CUDA(alloc(&M.xr, (size_t)M.max_rows * W * esz));
+  if (sc->loop_times > 0) {
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.x0), cap * W * 4));
+    ENG_CUDA(alloc(&M.xcat, cap * 2 * W * esz));
+  }
+  if (max_dec) ENG_CUDA(alloc(reinterpret_cast<void **>(&M.dec), cap * max_dec * 4));
+  if (max_vrot) ENG_CUDA(alloc(reinterpret_cast<void **>(&M.vrot), cap * max_vrot * 4));
+  if (stack_att_rec) {
+    M.attn_part_elems = (size_t)2048 * stack_att_rec;  // (tokens x slices) of one pass
+    ENG_CUDA(alloc(reinterpret_cast<void **>(&M.attn_part), M.attn_part_elems * 4));
+  }
   if (stack_lat_rec && !M.f32 && stack_tc) {
     bool ok = true;
     size_t max_D = 0, max_r = 0;
@@ -352,12 +516,18 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   }
   {
     // lightning: entry states of the segments of long spans (all layers share the buffer)
-    size_t seg = 0;
-    for (auto &L : M.layers)
+    size_t seg = 0, seg_a = 0;
+    for (auto &L : M.layers) {
       if (L.c.mixer == DIS_MIX_LIGHTNING && L.c.dim <= 128 && L.c.vdim <= 128)
         seg = std::max(seg, stack_lightning_seg_floats(cap_tokens, max_batch, L.c.heads, L.c.dim, L.c.vdim));
+      if (L.c.mixer == DIS_MIX_PARALLEL) {
+        seg = std::max(seg, stack_lightning_seg_floats(cap_tokens, max_batch, L.c.gla_heads, L.c.gla_dim, L.c.gla_vdim));
+        seg_a = std::max(seg_a, stack_lightning_seg_decay_floats(cap_tokens, max_batch, L.c.gla_heads, L.c.gla_dim));
+      }
+    }
     if (const char *g = getenv("DIS_STACK_LIGHT_SEGMENTS")) seg = atoi(g) != 0 ? seg : 0;
     if (seg) ENG_CUDA(alloc(reinterpret_cast<void **>(&M.light_seg), seg * 4));
+    if (seg && seg_a) ENG_CUDA(alloc(reinterpret_cast<void **>(&M.light_seg_a), seg_a * 4));
   }
   if (stack_lat_rec) {
     M.lat_part_elems = (size_t)2048 * stack_lat_rec;  // (tokens x slices) of one pass
@@ -392,7 +562,11 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
   // ---- pages: one pool per latent layer that owns a cache, rows of kv_rank + rot_dim elements; a page id is valid in all
   {
     size_t row_bytes = 0;
-    for (auto &L : M.layers) if (L.c.mixer == DIS_MIX_LATENT && L.c.kv_from < 0) row_bytes += (size_t)(L.c.kv_rank + L.c.rot_dim) * esz;
+    for (auto &R : M.runs) {
+      const dis_layer_config &lc = M.layers[(size_t)R.layer].c;
+      if (lc.mixer == DIS_MIX_LATENT && lc.kv_from < 0) row_bytes += (size_t)(lc.kv_rank + lc.rot_dim) * esz;
+      if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) row_bytes += (size_t)lc.kv_heads * (lc.dim + lc.vdim) * esz;
+    }
     int64_t want = c->kv_pages;
     const int64_t useful = (int64_t)max_batch * max_pages;
     if (want <= 0) {
@@ -404,9 +578,15 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     }
     if (want < 1) return fail(DIS_ERR_OUT_OF_MEMORY, "no device memory left for the latent pages");
     n_pages = want;
-    for (auto &L : M.layers)
-      if (L.c.mixer == DIS_MIX_LATENT && L.c.kv_from < 0)
-        ENG_CUDA(alloc(&L.pool, (size_t)n_pages * page_size * (L.c.kv_rank + L.c.rot_dim) * esz));
+    for (auto &R : M.runs) {
+      const dis_layer_config &lc = M.layers[(size_t)R.layer].c;
+      if (lc.mixer == DIS_MIX_LATENT && lc.kv_from < 0)
+        ENG_CUDA(alloc(&R.pool, (size_t)n_pages * page_size * (lc.kv_rank + lc.rot_dim) * esz));
+      if (lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL) {
+        ENG_CUDA(alloc(&R.kpool, (size_t)n_pages * page_size * lc.kv_heads * lc.dim * esz));
+        ENG_CUDA(alloc(&R.vpool, (size_t)n_pages * page_size * lc.kv_heads * lc.vdim * esz));
+      }
+    }
     pages_ix.init(page_size, n_pages, false);
     ENG_CUDA(alloc(reinterpret_cast<void **>(&d_page_table), (size_t)max_batch * max_pages * 4));
     stack_allocs.pop_back();  // freed with the engine's own buffers
@@ -447,11 +627,19 @@ int Engine::load_named(const char *nm, const void *host, int dtype, const int64_
     f.swap(g);
   }
   ENG_CUDA(cudaSetDevice(cfg.device));
-  if (t.dst->f32) ENG_CUDA(cudaMemcpy(reinterpret_cast<float *>(t.dst->ptr) + t.off, f.data(), n * 4, cudaMemcpyHostToDevice));
-  else {
+  // transform 2: the tensor is a block of columns of a wider matrix (row stride t.ld, first column t.off)
+  const bool block = t.transform == 2 && got.size() == 2;
+  const size_t cols = block ? (size_t)got[1] : n, rows = block ? (size_t)got[0] : 1, dpitch = block ? (size_t)t.ld : n;
+  if (t.dst->f32) {
+    float *dst = reinterpret_cast<float *>(t.dst->ptr) + t.off;
+    if (block) ENG_CUDA(cudaMemcpy2D(dst, dpitch * 4, f.data(), cols * 4, cols * 4, rows, cudaMemcpyHostToDevice));
+    else ENG_CUDA(cudaMemcpy(dst, f.data(), n * 4, cudaMemcpyHostToDevice));
+  } else {
     std::vector<uint16_t> b(n);
     for (size_t i = 0; i < n; i++) b[i] = float_to_bf16_bits(f[i]);
-    ENG_CUDA(cudaMemcpy(reinterpret_cast<uint16_t *>(t.dst->ptr) + t.off, b.data(), n * 2, cudaMemcpyHostToDevice));
+    uint16_t *dst = reinterpret_cast<uint16_t *>(t.dst->ptr) + t.off;
+    if (block) ENG_CUDA(cudaMemcpy2D(dst, dpitch * 2, b.data(), cols * 2, cols * 2, rows, cudaMemcpyHostToDevice));
+    else ENG_CUDA(cudaMemcpy(dst, b.data(), n * 2, cudaMemcpyHostToDevice));
   }
   t.loaded = true;
   return DIS_OK;
@@ -520,7 +708,7 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
   std::vector<int> take(idx.size());
   plan_mixed_step((int)idx.size(), rem.data(), max_prefill_tokens > 0 ? max_prefill_tokens : cap_tokens, cap_tokens, take.data());
   StepMeta &mt = meta_pre;
-  int T = 0, R = 0, SP = 0, QB = 0;
+  int T = 0, R = 0, SP = 0, QB = 0, KB = 0;
   stack_max_ctx = 0;
   stack_spans_h.clear();
   bool all_greedy = true;
@@ -564,6 +752,11 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
       mt.h<int>(mt.o_ab_len)[QB] = std::min(stack_bq, tk - j);
       QB++;
     }
+    for (int j = 0; j < tk && stack_abq > 0; j += stack_abq) {
+      mt.h<int>(mt.o_kb_tok0)[KB] = T + j;
+      mt.h<int>(mt.o_kb_len)[KB] = std::min(stack_abq, tk - j);
+      KB++;
+    }
     auto row = [&](int tok, float temp, float topp, uint64_t seed, uint64_t step) {
       mt.h<int>(mt.o_rowmap)[R] = tok;
       mt.h<float>(mt.o_temp)[R] = temp;
@@ -594,13 +787,25 @@ int Engine::stack_step(int n, const int *slots, int max_prefill_tokens, uint32_t
     sp = (stack_max_ctx + keys - 1) / keys;
     if (sp > 1 && (size_t)sp * T * stack_lat_rec <= M.lat_part_elems) { stack_lat_split = sp; stack_lat_keys = keys; }
   }
+  // paged attention likewise: one CTA per (query block, key/value head, slice)
+  stack_kb = KB;
+  stack_att_split = 1; stack_att_keys = 0;
+  if (KB > 0 && KB * stack_att_groups < kNumSMs && stack_max_ctx >= 256 && stack_att_rec) {
+    int sp = std::min(std::min((2 * kNumSMs + KB * stack_att_groups - 1) / (KB * stack_att_groups), stack_max_ctx / 64), 64);
+    if (sp > 1) {
+      const int keys = ((stack_max_ctx + sp - 1) / sp + 31) / 32 * 32;
+      sp = (stack_max_ctx + keys - 1) / keys;
+      if (sp > 1 && (size_t)sp * T * stack_att_rec <= M.attn_part_elems) { stack_att_split = sp; stack_att_keys = keys; }
+    }
+  }
   // A pass of single tokens only (decode rows, no kept prompt positions) has the same launches whenever its size, its
   // slicing and its sampler agree: the second such pass is captured into a CUDA graph and later ones replay it.
   const bool graphable = !(cfg.flags & DIS_FLAG_NO_GRAPH) && T == SP && R == T && T <= 0xFFFF;
   if (!graphable) {
     ENG_CUDA(stack_forward(T, SP, QB, R, all_greedy));
   } else {
-    const uint64_t key = (uint64_t)T | ((uint64_t)stack_lat_split << 16) | ((uint64_t)(stack_lat_keys / 32) << 24) | (all_greedy ? 1ull << 60 : 0ull);
+    const uint64_t key = (uint64_t)T | ((uint64_t)stack_lat_split << 16) | ((uint64_t)(stack_lat_keys / 32) << 24) |
+                         ((uint64_t)stack_att_split << 36) | ((uint64_t)(stack_att_keys / 32) << 43) | (all_greedy ? 1ull << 60 : 0ull);
     auto it = graphs.find(key);
     if (it != graphs.end() && it->second) {
       ENG_CUDA(cudaGraphLaunch(it->second, stream));
@@ -719,10 +924,37 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     kl++;
     return launch_stack_gemm(g, stream);
   };
-  RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, T, W, stream)); kl++;
-  const float *pend_y = nullptr, *pend_post = nullptr;
+  RET_CUDA(launch_stack_embed(M.embed.ptr, f32, sp.tokens, M.x, M.x0, M.c.embed_scale, T, W, stream)); kl++;
+  const float *pend_y = nullptr, *pend_post = nullptr, *pend_post_b = nullptr;
+  const bool ln = M.c.norm_kind == DIS_NORM_LAYER;
   const bool single = T == n_spans;  // every span one token long: the fused boundary kernel
-  auto sublayer_in = [&](const float *pre, const float *cw, float *cstate) -> cudaError_t {
+  // The boundary in front of a sublayer: the product before it joins the residual through its post norm, then the pre norm (and
+  // the convolution) makes the sublayer's input.  pre == null: only the residual is updated.  cat: [x ; x0] is written too.
+  auto sublayer_in = [&](const float *pre, const float *pre_b, const float *cw, float *cstate, bool cat = false) -> cudaError_t {
+    if (ln) {  // layer norms: one kernel for passes of any shape; it sums the slices of the product before and adds its bias
+      kl++;
+      const float *src = pend_y ? (pend_parts > 1 || pend_bias ? pend_src : pend_y) : nullptr;
+      const bool conv = pre && taps >= 1;
+      const cudaError_t e = launch_stack_boundary_ln(M.x, src, pend_parts, pend_stride, pend_bias, pend_post, pend_post_b, pre, pre_b,
+                                                     conv ? M.hn : nullptr, conv ? nullptr : M.hc, M.x0, cat ? M.xcat : nullptr, f32, T, W,
+                                                     eps, stream);
+      pend_y = nullptr; pend_parts = 1; pend_bias = nullptr;
+      if (e != cudaSuccess || !conv) return e;
+      kl += taps > 1 ? 2 : 1;
+      return launch_stack_canon(M.hn, cw, cstate, sp, M.hc, f32, W, taps, stream);
+    }
+    if (cat) {  // scalar-gain norms in front of a loop pass: the residual update alone, then [x ; x0]
+      if (single) {
+        kl++;
+        RET_CUDA(launch_stack_boundary_single(M.x, pend_y ? (pend_parts > 1 || pend_bias ? pend_src : pend_y) : nullptr, pend_parts, pend_stride,
+                                              pend_bias, pend_post, nullptr, nullptr, nullptr, sp, M.hc, f32, W, taps, eps, stream));
+        pend_parts = 1; pend_bias = nullptr;
+      } else if (pend_y) { RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++; }
+      pend_y = nullptr;
+      kl++;
+      return launch_stack_boundary_ln(M.x, nullptr, 1, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, M.x0, M.xcat, f32, T, W,
+                                      eps, stream);
+    }
     if (single) {
       kl++;
       const cudaError_t e = launch_stack_boundary_single(M.x, pend_y ? (pend_parts > 1 || pend_bias ? pend_src : pend_y) : nullptr, pend_parts,
@@ -737,21 +969,36 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     return launch_stack_copy_act(M.hn, M.hc, f32, (long long)T * W, stream);
   };
   const int lat_split = stack_lat_split, lat_keys = stack_lat_keys;
-  for (size_t li = 0; li < M.layers.size(); li++) {
-    StackLayer &L = M.layers[li];
+  const bool later = single || ln;  // the boundary kernel of the next sublayer sums a product's slices and adds its bias
+  auto norm_w = [&](StackLayer &L, int k) { return ln ? reinterpret_cast<const float *>(L.ln_w[k].ptr) : L.g4 + k; };
+  auto norm_b = [&](StackLayer &L, int k) { return ln ? reinterpret_cast<const float *>(L.ln_b[k].ptr) : nullptr; };
+  int max_span = 0;
+  for (auto &sh : stack_spans_h) max_span = std::max(max_span, sh.len);
+  for (size_t ri = 0; ri < M.runs.size(); ri++) {
+    StackRun &Rn = M.runs[ri];
+    StackLayer &L = M.layers[(size_t)Rn.layer];
     const dis_layer_config &lc = L.c;
-    RET_CUDA(sublayer_in(L.g4 + 0, L.canon1, L.cstate1));
+    if (Rn.loop_pass >= 0) {
+      // in front of a loop pass: x = loop_in [x ; x0] + loop_step[pass].  The boundary kernel adds the product before to the
+      // residual and writes [x ; x0]; the projection's result (with the pass's vector as its bias) replaces the residual.
+      RET_CUDA(sublayer_in(nullptr, nullptr, nullptr, nullptr, true));
+      RET_CUDA(gemm(M.xcat, f32, 2 * W, M.loop_in, 0, reinterpret_cast<const float *>(M.loop_step.ptr) + (size_t)Rn.loop_pass * W, M.x, T, W,
+                    2 * W, cap_tokens));
+    }
+    RET_CUDA(sublayer_in(norm_w(L, 0), norm_b(L, 0), L.canon1, Rn.cstate1));
     const int N = L.n_in;
     const float *in_bias = nullptr;  // minGRU adds its projections' biases itself when the product left them out
+    const bool is_attn = lc.mixer == DIS_MIX_ATTENTION || lc.mixer == DIS_MIX_PARALLEL;
     RET_CUDA(gemm(M.hc, f32, W, L.w_in, 0, L.b_in.ptr ? reinterpret_cast<const float *>(L.b_in.ptr) : nullptr, M.proj, T, N, W, cap_tokens,
-                  lc.mixer == DIS_MIX_MINGRU ? &in_bias : nullptr));
+                  lc.mixer == DIS_MIX_MINGRU || is_attn ? &in_bias : nullptr));
     int n_mix = 0;
+    const float *o_bias = nullptr;
     if (lc.mixer == DIS_MIX_LIGHTNING) {
       const int H = lc.heads, d = lc.dim, dv = lc.vdim;
       int max_len = 0;
       for (auto &sh : stack_spans_h) max_len = std::max(max_len, sh.len);
       const bool segments = M.light_seg && max_len > stack_lightning_seg_tokens() && d <= 128 && dv <= 128;
-      RET_CUDA(launch_stack_lightning(M.proj, N, reinterpret_cast<const float *>(L.decay_d.ptr), L.state, sp, M.mix, H, d, dv,
+      RET_CUDA(launch_stack_lightning(M.proj, N, reinterpret_cast<const float *>(L.decay_d.ptr), Rn.state, sp, M.mix, H, d, dv,
                                       segments ? M.light_seg : nullptr, max_len, stream));
       if (segments) kl += 2;
       RET_CUDA(launch_stack_norm_gate(M.mix, reinterpret_cast<const float *>(L.norm_w.ptr), M.proj + L.g_off, N, M.act, f32, T, H * dv, eps, stream));
@@ -760,14 +1007,38 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     } else if (lc.mixer == DIS_MIX_MINGRU) {
       int max_len = 0;
       for (auto &sh : stack_spans_h) max_len = std::max(max_len, sh.len);
-      RET_CUDA(launch_stack_mingru(M.proj, N, in_bias, L.state, sp, M.act, f32, lc.width, max_len, stream)); kl++;
+      RET_CUDA(launch_stack_mingru(M.proj, N, in_bias, Rn.state, sp, M.act, f32, lc.width, max_len, stream)); kl++;
       n_mix = lc.width;
+    } else if (is_attn) {
+      const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
+      const bool par = lc.mixer == DIS_MIX_PARALLEL;
+      StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, eps};
+      const float *qkn = reinterpret_cast<const float *>(L.qk_norm.ptr), *tpb = reinterpret_cast<const float *>(L.temp_pb.ptr);
+      RET_CUDA(launch_stack_attn_prep(M.proj, N, L.q_off, L.k_off, L.v_off, in_bias, qkn, qkn ? qkn + (size_t)H * d : nullptr, L.freq, L.vfreq, sa,
+                                      sp, M.qf, Rn.kpool, Rn.vpool, M.vrot, f32, d_page_table, max_pages, page_size, stream));
+      RET_CUDA(launch_stack_attn(M.qf, Rn.kpool, Rn.vpool, f32, tpb, tpb ? tpb + H : nullptr, sa, sp, mt.d<int>(mt.o_kb_tok0),
+                                 mt.d<int>(mt.o_kb_len), stack_kb, stack_abq, d_page_table, max_pages, page_size, M.act, L.n_act, 0,
+                                 par ? lc.mix_scale : 1.f, M.vrot, stack_att_split, stack_att_keys, M.attn_part, stream));
+      kl += stack_att_split > 1 ? 3 : 2;
+      if (par) {
+        const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim;
+        RET_CUDA(launch_stack_gla_decay(M.proj, N, L.ga_off, L.a2.ptr, L.a2.f32, reinterpret_cast<const float *>(L.a2_b.ptr), T, Hr * dr,
+                                        lc.gla_rank, lc.gla_tau, M.dec, stream));
+        const bool segments = M.light_seg && M.light_seg_a && max_span > stack_lightning_seg_tokens();
+        RET_CUDA(launch_stack_gla(M.proj, N, L.gq_off, L.gk_off, L.gv_off, M.dec, Rn.state, sp, M.mix, Hr, dr, dvr,
+                                  segments ? M.light_seg : nullptr, segments ? M.light_seg_a : nullptr, max_span, stream));
+        RET_CUDA(launch_stack_headnorm_silu(M.mix, reinterpret_cast<const float *>(L.gla_norm.ptr), M.proj + L.gg_off, N, M.act, L.n_act,
+                                            H * dv, lc.gla_scale, f32, T, Hr, dvr, eps, stream));
+        kl += segments ? 5 : 3;
+      }
+      o_bias = reinterpret_cast<const float *>(L.b_o.ptr);
+      n_mix = L.n_act;
     } else {
       const int H = lc.heads, d = lc.dim, dr = lc.rot_dim, dv = lc.vdim, r = lc.kv_rank, D = r + dr;
       StackLatent sl{H, d, dr, dv, r, lc.rot_dims, lc.rot_base, lc.scale, eps};
-      StackLayer &KV = M.layers[(size_t)L.kv_layer];
+      StackRun &KV = M.runs[(size_t)Rn.kv_run];
       RET_CUDA(launch_stack_latent_prep(M.proj, N, L.q_off, L.dkv_off, lc.kv_from < 0 ? reinterpret_cast<const float *>(L.norm_w.ptr) : nullptr, sl, sp,
-                                        M.qf, lc.kv_from < 0 ? L.pool : nullptr, f32, d_page_table, max_pages, page_size, stream));
+                                        M.qf, lc.kv_from < 0 ? Rn.pool : nullptr, f32, d_page_table, max_pages, page_size, stream));
       // absorbed queries: qf[t][h][0..r) = sum_a q[t][h][a] * uk[h*d + a][.]  (one batch entry per head).  Large bf16 passes:
       // one tensor-core product per head over the head's queries packed contiguously; else the batched fp32-FMA product.
       const bool head_tc = M.lat_gemm && T >= 256 && !L.ukT.f32 && !L.uv.f32 && d % 8 == 0 && ((size_t)r * d * 2) % 16 == 0 &&
@@ -846,16 +1117,16 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       kl += 5;
       n_mix = H * dv;
     }
-    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, nullptr, M.y, T, W, n_mix, cap_tokens, nullptr, single));
-    pend_y = M.y; pend_post = L.g4 + 1;
+    RET_CUDA(gemm(M.act, f32, n_mix, L.w_o, 0, o_bias, M.y, T, W, n_mix, cap_tokens, nullptr, later));
+    pend_y = M.y; pend_post = norm_w(L, 1); pend_post_b = norm_b(L, 1);
     if (lc.mlp == DIS_MLP_NONE) continue;
-    RET_CUDA(sublayer_in(L.g4 + 2, L.canon2, L.cstate2));
+    RET_CUDA(sublayer_in(norm_w(L, 2), norm_b(L, 2), L.canon2, Rn.cstate2));
     if (lc.mlp == DIS_MLP_DENSE) {
       const int ff = lc.ff;
       const float *gu_bias = nullptr;
       RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias));
-      RET_CUDA(launch_stack_glu(M.proj, gu_bias, M.act, f32, nullptr, T, ff, lc.limit, stream)); kl++;
-      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens, nullptr, single));
+      RET_CUDA(launch_stack_glu(M.proj, gu_bias, M.act, f32, nullptr, T, ff, lc.limit, lc.mlp_act, stream)); kl++;
+      RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens, nullptr, later));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
       RET_CUDA(launch_stack_route(M.hc, f32, reinterpret_cast<const float *>(L.router.ptr), T, W, E, top, M.r_idx, M.r_wt, stream));
@@ -878,7 +1149,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
           RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, stream));
           off += cnt; kl++;
         }
-        RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, stream));
+        RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
         off = 0;
         for (int e = 0; e < E; e++) {
           const int cnt = M.h_counts[e];
@@ -891,7 +1162,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
           off += cnt; kl++;
         }
         RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, M.y, T, W, top, stream));
-        pend_y = M.y; pend_post = L.g4 + 3;
+        pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
         continue;
       }
       const int tiles_cap = std::min(M.max_tiles, (rows + kStackGemmTile - 1) / kStackGemmTile + E);
@@ -901,7 +1172,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       g.out = M.proj; g.ldo = 2 * ff; g.M = rows; g.N = 2 * ff; g.K = W;
       g.tiles = M.tiles; g.max_tiles = tiles_cap;
       RET_CUDA(launch_stack_gemm(g, stream));
-      RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, stream));
+      RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
       StackGemm dn;
       dn.A = M.act; dn.a_f32 = f32; dn.lda = ff;
       dn.W = L.w_down.ptr; dn.w_f32 = L.w_down.f32; dn.ldw = ff; dn.w_bs = (long long)W * ff;
@@ -911,14 +1182,18 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       RET_CUDA(launch_stack_moe_combine(M.rows_out, M.where, M.r_wt, M.y, T, W, top, stream));
       kl += 6;
     }
-    pend_y = M.y; pend_post = L.g4 + 3;
+    pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);
   }
   // the last sublayer's output joins the residual; rows that need logits get the final norm and the head
-  if (single) RET_CUDA(sublayer_in(nullptr, nullptr, nullptr));
+  if (single || ln) RET_CUDA(sublayer_in(nullptr, nullptr, nullptr, nullptr));
   else { RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++; }
   if (R <= 0) return cudaSuccess;
-  RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream)); kl++;
+  if (ln) RET_CUDA(launch_stack_final_ln(M.x, mt.d<int>(mt.o_rowmap), reinterpret_cast<const float *>(M.final_w.ptr),
+                                         reinterpret_cast<const float *>(M.final_b.ptr), M.xr, f32, R, W, eps, stream));
+  else RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream));
+  kl++;
   RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W, M.max_rows));
+  if (M.c.logit_scale != 1.f) { RET_CUDA(launch_stack_scale(M.logits, (long long)R * M.c.vocab, M.c.logit_scale, stream)); kl++; }
   const float *temp = mt.d<float>(mt.o_temp), *topp = mt.d<float>(mt.o_topp);
   const unsigned long long *seed = mt.d<unsigned long long>(mt.o_seed), *step = mt.d<unsigned long long>(mt.o_step);
   float *d_logprob = reinterpret_cast<float *>(M.d_out + M.max_rows);

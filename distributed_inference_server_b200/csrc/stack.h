@@ -43,7 +43,9 @@ struct StackSpans {  // device arrays of the pass
   int T, n_spans;
 };
 
-cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, int T, int W, cudaStream_t st);
+// x = embed[token] * scale; x0 (when given) receives the same rows
+cudaError_t launch_stack_embed(const void *embed, bool f32, const uint32_t *tokens, float *x, float *x0, float scale, int T, int W,
+                               cudaStream_t st);
 // x += unit_rms(y) * post (when y), then hn = unit_rms(x) * pre (when hn).  post / pre: device scalars.
 cudaError_t launch_stack_resid_norm(float *x, const float *y, const float *post, const float *pre, float *hn, int T, int W,
                                     float eps, cudaStream_t st);
@@ -55,6 +57,15 @@ cudaError_t launch_stack_canon(const float *hn, const float *w, float *state, co
 cudaError_t launch_stack_boundary_single(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post,
                                          const float *pre, const float *cw, float *cstate, const StackSpans &sp, void *hc, bool f32,
                                          int W, int taps, float eps, cudaStream_t st);
+// The same boundary with layer norms (weight and bias vectors) in place of the scalar-gain RMS norms: y = bias + the n_part
+// slices; x += LN(y; post); cat (when given) = [x ; x0] in the compute type; LN(x; pre) -> hn (fp32, when given) and hc
+// (compute type, when given).  post / pre null: that step is left out.
+cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post_w,
+                                     const float *post_b, const float *pre_w, const float *pre_b, float *hn, void *hc, const float *x0,
+                                     void *cat, bool f32, int T, int W, float eps, cudaStream_t st);
+cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
+                                  float eps, cudaStream_t st);
+cudaError_t launch_stack_scale(float *v, long long n, float s, cudaStream_t st);
 cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st);
 // proj [T][ld]: q at 0, k at H*d, v at 2*H*d (pre-activation).  state [slots][H][d][dv].  o [T][H*dv] fp32.
 // seg (or null): room for stack_lightning_seg_floats() floats -- spans longer than stack_lightning_seg_tokens() (max_len: the
@@ -63,6 +74,41 @@ size_t stack_lightning_seg_floats(int cap_tokens, int max_spans, int H, int d, i
 int stack_lightning_seg_tokens();
 cudaError_t launch_stack_lightning(const float *proj, long long ld, const float *decay, float *state, const StackSpans &sp,
                                    float *o, int H, int d, int dv, float *seg, int max_len, cudaStream_t st);
+// Gated linear attention (per-channel decay): S = diag(a_t) S + k_t v_t^T, o_t = S^T (q_t / sqrt(d)).
+// decays: dec[t][c] = sigmoid(z)^(1/tau), z = b[c] + sum_r a2[c][r] * proj[t][a_off + r]; n = H*d channels.
+cudaError_t launch_stack_gla_decay(const float *proj, long long ld, int a_off, const void *a2, bool w_f32, const float *b, int T, int n,
+                                   int rank, float tau, float *dec, cudaStream_t st);
+// proj [T][ld] with q, k [H][d] and v [H][dv] at the given columns; dec [T][H*d]; state [slots][H][d][dv]; o [T][H*dv] fp32.
+// seg / seg_a: as for lightning, plus room for stack_lightning_seg_decay_floats() floats (the segments' decay products).
+size_t stack_lightning_seg_decay_floats(int cap_tokens, int max_spans, int H, int d);
+cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *dec, float *state,
+                             const StackSpans &sp, float *o, int H, int d, int dv, float *seg, float *seg_a, int max_len,
+                             cudaStream_t st);
+// out[t][off + h*dv + j] = scale * unit_rms_over_head(o[t][h])[j] * w[j] * silu(gate[t][h*dv + j]); out [T][ldo] compute type
+cudaError_t launch_stack_headnorm_silu(const float *o, const float *w, const float *gate, long long ldg, void *out, long long ldo,
+                                       int off, float scale, bool f32, int T, int H, int dv, float eps, cudaStream_t st);
+// Attention over paged keys and values (k_stack_attn.cu).
+struct StackAttn {
+  int H, G, d, dv, rot_dims;
+  unsigned flags;  // DIS_ATTN_*
+  float scale, eps;
+};
+// Per token: (bias), query/key norm over the whole projection, rotation of the first rot_dims coordinates of every head by
+// pos * freq[i] (pairs i, i + rot_dims/2); queries to qf [T][H*d]; rotated keys and the values (own projection at v_off, or the
+// unrotated keys; rotated by pos * vfreq[m] over pairs m, m + dv/2 with DIS_ATTN_ROT_V) to the token's row of the pools
+// ([pages*page_size][G*d] and [..][G*dv]); vrot [T][dv] receives cos | sin of the value angles for the output's rotation back.
+cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, int k_off, int v_off, const float *bias, const float *qn,
+                                   const float *kn, const double *freq, const double *vfreq, const StackAttn &c, const StackSpans &sp,
+                                   float *qf, void *kpool, void *vpool, float *vrot, bool f32, const int *page_table, int max_pages,
+                                   int page_size, cudaStream_t st);
+// query blocks hold at most stack_attn_block_tokens() tokens of one span; n_split > 1: slices of keys_per_split keys (a multiple
+// of 32), records of dv + 2 floats per (slice, token, head) in `part`, merged by a second kernel.  The result, times out_scale
+// and rotated back when values were rotated, lands in out [T][ld_out] (compute type) at columns out_off + h * dv.
+int stack_attn_block_tokens(const StackAttn &c);
+cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vpool, bool f32, const float *temp, const float *pb,
+                              const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, int bq,
+                              const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
+                              float out_scale, const float *vrot, int n_split, int keys_per_split, float *part, cudaStream_t st);
 // out = unit_rms(o) * w * sigmoid(gate) per token over n = H*dv coordinates; gate [T][ldg]
 cudaError_t launch_stack_norm_gate(const float *o, const float *w, const float *gate, long long ldg, void *out, bool f32, int T,
                                    int n, float eps, cudaStream_t st);
@@ -104,10 +150,11 @@ cudaError_t launch_stack_latent_gather(const void *pool, const int *pt_row, int 
                                        uint16_t *cg, uint16_t *cgt, cudaStream_t st);
 cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const float *sink, int H, int pos_first, float scale,
                                         uint16_t *P, cudaStream_t st);
-// act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu [M][2*ff] (gate | up)
+// kind DIS_ACT_CLAMPED: act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit);
+// DIS_ACT_GELU_TANH: act = gelu_tanh(g) u.  gu [M][2*ff] (gate | up)
 // bias (or null): [2*ff], added to gu here when the product that made gu left it out
 cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
-                             cudaStream_t st);
+                             int kind, cudaStream_t st);
 // Router: logits in fp32 from hc and the fp32 router matrix; top-k by value (lowest index wins a tie); softmax over the chosen.
 cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
                                cudaStream_t st);
@@ -147,23 +194,52 @@ struct StackLayer {
   StackTensor sink;     // latent: [H] fp32
   StackTensor decay_d;  // lightning: [H] fp32
   int n_in = 0, q_off = 0, dkv_off = 0, g_off = 0;
-  int kv_layer = -1;    // latent: index of the layer whose pool this layer reads (itself when it owns one)
-  void *pool = nullptr; // latent with a pool of its own
-  float *state = nullptr;   // lightning [slots][H][d][dv]; mingru [slots][n]
   float *canon1 = nullptr, *canon2 = nullptr;        // [W][taps] fp32
-  float *cstate1 = nullptr, *cstate2 = nullptr;      // [slots][taps-1][W]
-  float *g4 = nullptr;  // device: norm1, norm1b, norm2, norm2b
+  float *g4 = nullptr;  // device: norm1, norm1b, norm2, norm2b (scalar gains)
+  StackTensor ln_w[4], ln_b[4];  // the same four norms as layer norms: weight and bias vectors [W] fp32
+  // attention (alone, or the first half of a parallel mixer): w_in rows q | k | v; qf columns follow the same order
+  int k_off = 0, v_off = 0;
+  StackTensor qk_norm;   // [H*d + G*d] fp32: gains of the whole-projection query and key norms
+  StackTensor temp_pb;   // [2H] fp32: per-head factor on the score, then per-head bias under the sigmoid
+  StackTensor b_o;       // [W] fp32: bias of the output projection
+  double *freq = nullptr, *vfreq = nullptr;  // device: rotary frequencies [rot_dims/2] (scaled) and value frequencies [vdim/2]
+  int n_act = 0;         // columns of the output projection's input: H*vdim (+ gla_heads*gla_vdim behind them)
+  // gated linear attention (second half of a parallel mixer): w_in rows q | k | v | g | bottleneck behind the attention's
+  int gq_off = 0, gk_off = 0, gv_off = 0, gg_off = 0, ga_off = 0;
+  StackTensor a2, a2_b, gla_norm;  // [Hd][rank] compute type, [Hd] fp32, [gla_vdim] fp32
   // feed-forward
   StackTensor w_gu, b_gu, w_down, b_down;  // dense: [2ff][W], [2ff], [W][ff], [W]; experts: stacked per expert
   StackTensor router;                      // [E][W] fp32
+};
+
+// One execution of a layer inside a forward pass.  Without a loop every layer runs once; a looped stretch contributes one
+// run per pass and layer, all reading the layer's weights, each with its own recurrent state and cache.
+struct StackRun {
+  int layer = 0;
+  int loop_pass = -1;       // t >= 0: the first layer of loop pass t (the loop's input projection runs in front of it)
+  int kv_run = -1;          // latent: the run whose pool this run reads (itself when it owns one)
+  void *pool = nullptr;     // latent with a pool of its own: [pages*page_size][kv_rank + rot_dim]
+  void *kpool = nullptr, *vpool = nullptr;  // attention: [pages*page_size][G*dim], [..][G*vdim]
+  float *state = nullptr;   // lightning / gated linear attention [slots][H][d][dv]; mingru [slots][n]
+  float *cstate1 = nullptr, *cstate2 = nullptr;      // [slots][taps-1][W]
 };
 
 struct StackModel {
   dis_stack_config c{};
   bool f32 = false;
   std::vector<StackLayer> layers;
+  std::vector<StackRun> runs;
   StackTensor embed, head;
   float *final_g = nullptr;
+  StackTensor final_w, final_b;    // layer-norm form of the final norm
+  StackTensor loop_in, loop_step;  // [W][2W] compute type, [times][W] fp32
+  float *x0 = nullptr;             // the scaled embedding rows of the pass (input of every loop pass)
+  void *xcat = nullptr;            // [x ; x0] in the compute type
+  float *dec = nullptr;            // gated linear attention: the decays of the pass [T][H*d]
+  float *vrot = nullptr;           // attention with rotated values: cos | sin of every token's value angles [T][vdim]
+  float *attn_part = nullptr;      // attention: slice records
+  size_t attn_part_elems = 0;
+  float *light_seg_a = nullptr;    // gated linear attention: decay products of the segments of long spans
   std::vector<StackTensor *> views;  // named scalars and taps: tensors that point into areas owned elsewhere
   int max_rows = 0;
   // activations

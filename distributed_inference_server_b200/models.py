@@ -9,6 +9,13 @@ engine's description of the model and names every tensor.  Two families exist:
             with a fixed per-head decay, a minimal gated recurrence, or latent attention over a compressed cache (which a
             later layer may share), and a dense or mixture-of-experts feed-forward, every sublayer behind a scalar-gain RMS
             norm and a short causal convolution.
+  Motolix   a layer-list decoder of the same engine with layer norms (weight and bias) before and after every sublayer, a
+            stretch of layers that runs several times with shared weights (each pass with its own cache and state, entered
+            through a projection of [residual ; embedding] plus a per-pass vector), and two mixers: `attention` (grouped-query,
+            values = unrotated keys, partial rotary with wavelength-dependent frequency scaling, sigmoid weights with a
+            per-head temperature and bias instead of softmax) and `parallel` (softmax attention with whole-projection
+            query/key norms and position-rotated values, beside gated linear attention with a per-channel decay; the two
+            outputs are added with fixed weights); feed-forward gelu_tanh(gate) * up.
 
 The reference has no model loading at all (crates/inference/src/worker.rs:1 is empty).
 """
@@ -25,7 +32,8 @@ import numpy as np
 
 from . import binding as B
 
-_MIXERS = {"lightning": B.MIX_LIGHTNING, "mingru": B.MIX_MINGRU, "latent_attention": B.MIX_LATENT}
+_MIXERS = {"lightning": B.MIX_LIGHTNING, "mingru": B.MIX_MINGRU, "latent_attention": B.MIX_LATENT,
+           "attention": B.MIX_ATTENTION, "parallel": B.MIX_PARALLEL}
 
 
 @dataclass
@@ -47,6 +55,21 @@ class LayerSpec:
     experts: int = 0
     top: int = 0
     limit: float = 0.0
+    # attention / parallel
+    kv_heads: int = 0
+    attn_flags: int = 0
+    rot_factor: float = 0.0
+    rot_low: float = 0.0
+    rot_high: float = 0.0
+    rot_original: int = 0
+    gla_heads: int = 0
+    gla_dim: int = 0
+    gla_vdim: int = 0
+    gla_rank: int = 0
+    gla_tau: float = 1.0
+    mix_scale: float = 1.0
+    gla_scale: float = 1.0
+    mlp_act: str = "clamped"  # clamped (with biases) | gelu_tanh (without)
 
 
 @dataclass
@@ -58,13 +81,35 @@ class StackSpec:
     layers: List[LayerSpec]
     canon_taps: int = 0
     norm_eps: float = 1e-5
+    norm_kind: str = "rms_scalar"  # rms_scalar | layer
+    embed_scale: float = 1.0
+    logit_scale: float = 1.0
+    loop: Tuple[int, int, int] = (0, 0, 0)  # start, stop, times (times 0 = no loop)
+
+    def layer_runs(self) -> List[int]:
+        """Layer index of every layer run of one forward pass, the looped stretch repeated."""
+        a, b, n = self.loop
+        if n <= 0:
+            return list(range(len(self.layers)))
+        return list(range(a)) + list(range(a, b)) * n + list(range(b, len(self.layers)))
 
     def tensor_shapes(self) -> Dict[str, Tuple[int, ...]]:
         """Every tensor of the model file, by name."""
-        W, out = self.width, {"embed": (self.vocab, self.width), "head": (self.vocab, self.width), "final.norm": ()}
+        W, out = self.width, {"embed": (self.vocab, self.width), "head": (self.vocab, self.width)}
+        vec = self.norm_kind == "layer"
+
+        def norm(name):
+            out[name] = (W,) if vec else ()
+            if vec:
+                out[name + ".b"] = (W,)
+        norm("final.norm")
+        if self.loop[2] > 0:
+            out["loop.in"] = (W, 2 * W)
+            out["loop.step"] = (self.loop[2], W)
         for i, L in enumerate(self.layers):
             p = f"l{i}."
-            out[p + "norm1"] = out[p + "norm1b"] = ()
+            norm(p + "norm1")
+            norm(p + "norm1b")
             if self.canon_taps >= 1:
                 out[p + "canon1"] = (W, self.canon_taps)
             if L.mixer == "lightning":
@@ -73,6 +118,21 @@ class StackSpec:
             elif L.mixer == "mingru":
                 out.update({p + "mix.z": (L.width, W), p + "mix.z.b": (L.width,), p + "mix.x": (L.width, W), p + "mix.x.b": (L.width,),
                             p + "mix.g": (L.width, W), p + "mix.o": (W, L.width)})
+            elif L.mixer in ("attention", "parallel"):
+                a = p + ("mix.left." if L.mixer == "parallel" else "mix.")
+                out.update({a + "q": (L.heads * L.dim, W), a + "k": (L.kv_heads * L.dim, W), a + "o": (W, L.heads * L.vdim)})
+                if not L.attn_flags & B.ATTN_V_IS_K:
+                    out[a + "v"] = (L.kv_heads * L.vdim, W)
+                if L.attn_flags & B.ATTN_BIAS:
+                    out.update({a + "q.b": (L.heads * L.dim,), a + "k.b": (L.kv_heads * L.dim,), a + "o.b": (W,)})
+                if L.attn_flags & B.ATTN_QK_NORM:
+                    out.update({a + "q.norm": (L.heads * L.dim,), a + "k.norm": (L.kv_heads * L.dim,)})
+                if L.attn_flags & B.ATTN_SIGMOID:
+                    out.update({a + "temp": (L.heads,), a + "pb": (L.heads,)})
+                if L.mixer == "parallel":
+                    r, n, nv = p + "mix.right.", L.gla_heads * L.gla_dim, L.gla_heads * L.gla_vdim
+                    out.update({r + "q": (n, W), r + "k": (n, W), r + "v": (nv, W), r + "g": (nv, W), r + "o": (W, nv),
+                                r + "norm": (L.gla_vdim,), r + "a1": (L.gla_rank, W), r + "a2": (n, L.gla_rank), r + "a2.b": (n,)})
             else:
                 out[p + "mix.q"] = (L.heads * (L.dim + L.rot_dim), W)
                 if L.kv_from < 0:
@@ -82,10 +142,13 @@ class StackSpec:
                             p + "mix.sink": (L.heads,), p + "mix.g": (L.heads * L.vdim, W), p + "mix.o": (W, L.heads * L.vdim)})
             if L.mlp == "none":
                 continue
-            out[p + "norm2"] = out[p + "norm2b"] = ()
+            norm(p + "norm2")
+            norm(p + "norm2b")
             if self.canon_taps >= 1:
                 out[p + "canon2"] = (W, self.canon_taps)
-            if L.mlp == "dense":
+            if L.mlp == "dense" and L.mlp_act == "gelu_tanh":
+                out.update({p + "mlp.gate": (L.ff, W), p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff)})
+            elif L.mlp == "dense":
                 out.update({p + "mlp.gate": (L.ff, W), p + "mlp.gate.b": (L.ff,), p + "mlp.up": (L.ff, W), p + "mlp.up.b": (L.ff,),
                             p + "mlp.down": (W, L.ff), p + "mlp.down.b": (W,)})
             else:
@@ -110,8 +173,15 @@ class StackSpec:
                 c.decay = d
             c.mlp = {"none": B.MLP_NONE, "dense": B.MLP_DENSE, "moe": B.MLP_MOE}[L.mlp]
             c.ff, c.experts, c.top, c.limit = L.ff, L.experts, L.top, L.limit
+            c.kv_heads, c.attn_flags = L.kv_heads, L.attn_flags
+            c.rot_factor, c.rot_low, c.rot_high, c.rot_original = L.rot_factor, L.rot_low, L.rot_high, L.rot_original
+            c.gla_heads, c.gla_dim, c.gla_vdim, c.gla_rank = L.gla_heads, L.gla_dim, L.gla_vdim, L.gla_rank
+            c.gla_tau, c.mix_scale, c.gla_scale = L.gla_tau, L.mix_scale, L.gla_scale
+            c.mlp_act = {"clamped": B.ACT_CLAMPED, "gelu_tanh": B.ACT_GELU_TANH}[L.mlp_act]
         sc = B.StackConfig(self.vocab, self.width, len(self.layers), self.canon_taps, max_ctx, max_logit_rows,
-                           B.F32 if f32 else B.BF16, self.norm_eps, arr)
+                           B.F32 if f32 else B.BF16, self.norm_eps, arr,
+                           {"rms_scalar": B.NORM_RMS_SCALAR, "layer": B.NORM_LAYER}[self.norm_kind],
+                           self.embed_scale, self.logit_scale, *self.loop)
         return sc, keep
 
 
@@ -153,6 +223,58 @@ def kidolorn_spec(cfg: dict) -> StackSpec:
                      float((cfg.get("norm") or {}).get("eps", 1e-5)))
 
 
+def _attention_fields(L: LayerSpec, mx: dict, flags: int, where: str) -> None:
+    L.heads, L.kv_heads, L.dim, L.vdim = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
+    if L.heads % L.kv_heads:
+        raise ValueError(f"{where}: heads must be a multiple of kv_heads")
+    rot = mx.get("rot") or {}
+    L.rot_dims, L.rot_base = int(rot.get("dims", 0)), float(rot.get("base", 10000.0))
+    sc = rot.get("scaling")
+    if sc:
+        L.rot_factor, L.rot_low, L.rot_high = float(sc["factor"]), float(sc["low"]), float(sc["high"])
+        L.rot_original = int(sc["original"])
+    L.scale = float(mx["scale"])
+    L.attn_flags = flags
+
+
+def motolix_spec(cfg: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> StackSpec:
+    """Motolix's config.json -> StackSpec.  Sizes the configuration does not state (the rank of the decay bottleneck of the
+    gated-linear half) come from the shapes of the model file's tensors, or from a `rank` entry beside the other sizes."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        kind, mx = ly["type"], ly["mixer"]
+        if kind == "attention":
+            L = LayerSpec("attention")
+            _attention_fields(L, mx, B.ATTN_SIGMOID | B.ATTN_V_IS_K | B.ATTN_BIAS, f"layer {i}")
+        elif kind == "parallel":
+            L = LayerSpec("parallel")
+            _attention_fields(L, mx["left"], B.ATTN_QK_NORM | B.ATTN_ROT_V, f"layer {i}")
+            r = mx["right"]
+            L.gla_heads, L.gla_dim, L.gla_vdim, L.gla_tau = int(r["heads"]), int(r["dim"]), int(r["vdim"]), float(r["tau"])
+            a1 = (shapes or {}).get(f"l{i}.mix.right.a1")
+            if a1 is not None:
+                L.gla_rank = int(a1[0])
+            elif "rank" in r:
+                L.gla_rank = int(r["rank"])
+            else:
+                raise ValueError(f"layer {i}: the rank of the decay projection is given by neither a tensor nor the configuration")
+            L.mix_scale, L.gla_scale = float(mx["left_scale"]), float(mx["right_scale"])
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        ml = ly.get("mlp")
+        if ml is not None:
+            if ml["kind"] != "dense":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {ml['kind']!r}")
+            L.mlp, L.ff, L.mlp_act = "dense", int(ml["ff"]), "gelu_tanh"
+        layers.append(L)
+    lp = cfg.get("loop")
+    loop = (int(lp["start"]), int(lp["stop"]), int(lp["times"])) if lp else (0, 0, 0)
+    if loop[2] > 0 and not 0 <= loop[0] < loop[1] <= len(layers):
+        raise ValueError("loop: start < stop must lie inside the layer list")
+    return StackSpec("Motolix", int(cfg["vocab"]), int(cfg["width"]), layers, 0, float((cfg.get("norm") or {}).get("eps", 1e-5)),
+                     "layer", float((cfg.get("embedding") or {}).get("scale", 1.0)), float(cfg.get("logit_scale", 1.0)), loop)
+
+
 def llama_shape(cfg: dict):
     """A Hugging Face style Llama config.json -> ModelShape."""
     from .worker import ModelShape
@@ -164,8 +286,9 @@ def llama_shape(cfg: dict):
 
 
 # architecture name -> (family, configuration reader)
-ARCHITECTURES: Dict[str, Tuple[str, Callable[[dict], object]]] = {
+ARCHITECTURES: Dict[str, Tuple[str, Callable[..., object]]] = {
     "Kidolorn": ("stack", kidolorn_spec),
+    "Motolix": ("stack", motolix_spec),
     "LlamaForCausalLM": ("llama", llama_shape),
     "llama": ("llama", llama_shape),
 }
@@ -182,7 +305,18 @@ def read_config(model_dir: str):
     """(family, description) of the model in `model_dir`."""
     cfg = json.load(open(os.path.join(model_dir, "config.json")))
     family, reader = ARCHITECTURES[architecture_of(cfg)]
+    if reader is motolix_spec:
+        st = os.path.join(model_dir, "model.safetensors")
+        return family, reader(cfg, safetensors_shapes(st) if os.path.exists(st) else None)
     return family, reader(cfg)
+
+
+def safetensors_shapes(path: str) -> Dict[str, Tuple[int, ...]]:
+    """name -> shape of every tensor of a safetensors file (the header only)."""
+    with open(path, "rb") as f:
+        n = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(n))
+    return {k: tuple(int(d) for d in v["shape"]) for k, v in header.items() if k != "__metadata__"}
 
 
 _ST_DTYPES = {"BF16": (np.uint16, B.BF16), "F32": (np.float32, B.F32), "I32": (np.int32, None)}
@@ -278,6 +412,16 @@ def random_tensors(spec: StackSpec, seed: int = 0, scale: float = 1.0) -> Dict[s
         leaf = name.rsplit(".", 1)[-1]
         if shape == ():
             a = np.asarray(rng.uniform(0.5, 1.5), np.float32)
+        elif leaf in ("norm1", "norm1b", "norm2", "norm2b") or name == "final.norm" or name.endswith(("q.norm", "k.norm")):
+            a = rng.uniform(0.5, 1.5, shape).astype(np.float32)
+        elif leaf == "temp":
+            a = rng.uniform(0.5, 1.5, shape).astype(np.float32)
+        elif leaf == "pb":
+            a = rng.normal(-2.0, 1.0, shape).astype(np.float32)
+        elif name == "loop.step":
+            a = rng.normal(0, 0.3, shape).astype(np.float32)
+        elif name.endswith("a2.b"):
+            a = rng.normal(2.0, 1.5, shape).astype(np.float32)
         elif leaf.startswith("canon"):
             a = rng.normal(0, 0.3, shape).astype(np.float32)
         elif leaf in ("norm",) or name.endswith("dkv.norm"):

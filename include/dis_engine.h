@@ -31,7 +31,7 @@ extern "C" {
 #endif
 
 #define DIS_API __attribute__((visibility("default")))
-#define DIS_ABI_VERSION 2 /* 2: 16-byte request ids, logprob on token events / callback, dis_serving_cancel */
+#define DIS_ABI_VERSION 3 /* 2: 16-byte request ids, logprob on token events / callback, dis_serving_cancel; 3: dis_layer_config and dis_stack_config grew (attention and parallel mixers, layer norms, layer loops) */
 
 /* ---- status codes: WorkerError, crates/core/src/error.rs:115-128 ------------------------------ */
 typedef enum dis_status {
@@ -413,18 +413,38 @@ DIS_API int dis_k_synth_bf16(uint16_t *dst, size_t n, uint64_t seed, int32_t kin
 /* ---- layer-list decoders ------------------------------------------------------------------------ *
  * A second model family beside the Llama decoder: the model is a list of layers, each one token mixer plus an
  * optional feed-forward.  Every layer is  x += post1(mixer(conv(pre1(x))));  x += post2(ff(conv(pre2(x))))  with
- * scalar-gain RMS norms and a short causal depthwise convolution (canon_taps taps, 0 = none) in front of each
- * sublayer.  The engine's sequences, pages, step planner, sampler and serving loop are the same as for Llama;
+ * four norms (norm_kind: scalar-gain RMS norms, or layer norms with weight and bias) and a short causal depthwise
+ * convolution (canon_taps taps, 0 = none) in front of each sublayer.  A stretch of layers may be run several times
+ * with the same weights (loop_*).  The engine's sequences, pages, step planner, sampler and serving loop are the same as for Llama;
  * sequences additionally own a slot of recurrent state (linear-attention matrices, gated-recurrence vectors and
  * the convolutions' last inputs).  The reference has no counterpart (its model family is Llama only). */
 typedef enum dis_mixer_kind {
   DIS_MIX_LIGHTNING = 0, /* linear attention, fixed decay per head: S = a S + k v^T, o = S^T q; q, k, v through SiLU; head-wise
                             outputs RMS-normed together, gated by a sigmoid */
   DIS_MIX_MINGRU = 1,    /* S = (1 - z) S + z c with z, c from the current token only; output S * silu(gate) */
-  DIS_MIX_LATENT = 2     /* softmax attention over a cached low-rank latent + one rotated key part shared by the heads,
+  DIS_MIX_LATENT = 2,    /* softmax attention over a cached low-rank latent + one rotated key part shared by the heads,
                             with a per-head sink term in the denominator and a sigmoid output gate */
+  DIS_MIX_ATTENTION = 3, /* grouped-query attention over paged keys and values; what it does beyond q k^T -> weights -> values
+                            is chosen by attn_flags */
+  DIS_MIX_PARALLEL = 4   /* two mixers read the same input: DIS_MIX_ATTENTION (the fields above) and gated linear attention
+                            (the gla_* fields); their outputs are added with the weights mix_scale / gla_scale */
 } dis_mixer_kind;
 typedef enum dis_mlp_kind { DIS_MLP_NONE = 0, DIS_MLP_DENSE = 1, DIS_MLP_MOE = 2 } dis_mlp_kind;
+/* Feed-forward unit.  CLAMPED: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, +-limit), biases on every
+ * matrix.  GELU_TANH: gelu_tanh(g) u, no biases. */
+typedef enum dis_mlp_act { DIS_ACT_CLAMPED = 0, DIS_ACT_GELU_TANH = 1 } dis_mlp_act;
+/* Norms around the sublayers.  RMS_SCALAR: x / rms(x) times one scalar gain (tensor of shape []).  LAYER: (x - mean) / sqrt(var +
+ * eps) * w + b with vectors w ("<name>") and b ("<name>.b"). */
+typedef enum dis_norm_kind { DIS_NORM_RMS_SCALAR = 0, DIS_NORM_LAYER = 1 } dis_norm_kind;
+/* dis_layer_config.attn_flags */
+#define DIS_ATTN_SIGMOID   1u   /* weight of a visible key = sigmoid(score * temp[h] + pb[h]) (per-head tensors "temp", "pb"),
+                                   not normalised over the keys; without the flag: softmax over the visible keys */
+#define DIS_ATTN_QK_NORM   2u   /* q and k (all heads together, before the split into heads and before rotation) are divided by
+                                   their root mean square and multiplied by "q.norm" / "k.norm" */
+#define DIS_ATTN_V_IS_K    4u   /* no value projection: the values are the keys as projected, before rotation */
+#define DIS_ATTN_ROT_V     8u   /* the value at position j is rotated by j over all vdim coordinates (pairs m, m + vdim/2, angle
+                                   j * rot_base^(-2m/vdim)) before it is cached, and a head's output at position i is rotated by -i */
+#define DIS_ATTN_BIAS     16u   /* q, k and the output projection carry biases ("q.b", "k.b", "o.b") */
 
 typedef struct dis_layer_config {
   int32_t mixer;                 /* dis_mixer_kind */
@@ -439,6 +459,20 @@ typedef struct dis_layer_config {
   int32_t ff;                    /* hidden size of the feed-forward (of one expert) */
   int32_t experts, top;          /* mixture of experts: how many, how many per token */
   float limit;                   /* clamp of the gate (above) and up (both sides) branches */
+  /* attention (DIS_MIX_ATTENTION, and the first half of DIS_MIX_PARALLEL): heads, dim, vdim, rot_dims, rot_base, scale above */
+  int32_t kv_heads;              /* key/value heads; query head h reads head h / (heads / kv_heads) */
+  uint32_t attn_flags;           /* DIS_ATTN_* */
+  float rot_factor, rot_low, rot_high; /* frequency scaling by wavelength l = 2 pi / f against rot_original: l < original/high
+                                    keeps f, l > original/low uses f / factor, between them the blend (1 - s) f / factor + s f
+                                    with s = (original / l - low) / (high - low); rot_factor 0 = none */
+  int32_t rot_original;
+  /* gated linear attention (second half of DIS_MIX_PARALLEL): per head S = diag(a_t) S + k_t v_t^T, o_t = S^T q_t with
+   * q scaled by gla_dim^(-1/2), a_t = sigmoid(z_t)^(1/gla_tau), z_t = A2 (A1 h) + b through a rank-gla_rank bottleneck; o is
+   * RMS-normed per head (one gain vector of gla_vdim), multiplied by silu(G h) and projected */
+  int32_t gla_heads, gla_dim, gla_vdim, gla_rank;
+  float gla_tau;
+  float mix_scale, gla_scale;    /* DIS_MIX_PARALLEL: weights of the two halves' outputs */
+  int32_t mlp_act;               /* dis_mlp_act */
 } dis_layer_config;
 
 typedef struct dis_stack_config {
@@ -449,12 +483,20 @@ typedef struct dis_stack_config {
   int32_t compute_dtype;         /* DIS_BF16: matrices and their inputs in bf16, fp32 accumulation; DIS_F32: everything fp32 */
   float norm_eps;
   const dis_layer_config *layers;
+  int32_t norm_kind;             /* dis_norm_kind of the four norms of a layer and of the final norm */
+  float embed_scale;             /* factor on the embedding row (0 is read as 1) */
+  float logit_scale;             /* factor on the logits (0 is read as 1) */
+  /* Layers loop_start .. loop_stop-1 run loop_times times in a row with the same weights (0 = no loop); every pass has its own
+   * cache and recurrent state.  In front of pass t the residual becomes "loop.in" [x ; x0] + "loop.step"[t], x0 being the scaled
+   * embedding ("loop.in": [width][2 width], "loop.step": [loop_times][width]). */
+  int32_t loop_start, loop_stop, loop_times;
 } dis_stack_config;
 
 /* cfg->model is ignored (model_info reports vocab, width, layers and max_ctx of the stack); tensor parallelism and the
  * prefix cache are not available for this family and are refused. */
 DIS_API int dis_engine_create_stack(const dis_engine_config *cfg, const dis_stack_config *stack, dis_engine **out);
-/* Tensors by the names of the model's file: "embed", "head", "final.norm", "l<i>.norm1", "l<i>.mix.q", "l<i>.mlp.e<j>.up", ...
+/* Tensors by the names of the model's file: "embed", "head", "final.norm", "l<i>.norm1", "l<i>.mix.q", "l<i>.mlp.e<j>.up",
+ * "l<i>.mix.left.q" / "l<i>.mix.right.a1" (the halves of a parallel mixer), ...
  * `shape` is checked against the configuration.  dtype: DIS_F32 values or DIS_BF16 bit patterns. */
 DIS_API int dis_engine_load_named(dis_engine *e, const char *name, const void *host, int dtype, const int64_t *shape,
                                   int32_t ndim);
