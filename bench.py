@@ -836,6 +836,92 @@ def run_kidolorn(args):
     return 0
 
 
+def run_motolix(args):
+    """Prefill and decode throughput of Motolix (layer norms, a looped stretch of layers, sigmoid attention whose values are its
+    keys, softmax attention with rotated values beside gated linear attention) next to the Llama decoder at equal width,
+    feed-forward size, vocabulary and number of layer runs; random weights, one GPU, measured like --workload kidolorn:
+    one pass over `batch` prompts of `prompt_len` tokens, then K decode steps of the batch, timed by the engine's CUDA
+    events around each pass (metadata upload and token read-back included).  Weights exceed L2 at every size."""
+    from distributed_inference_server_b200 import Engine, InferenceParams, ModelShape, WorkerConfig, models
+    from distributed_inference_server_b200.binding import FLAG_NO_GRAPH as B_FLAG_NO_GRAPH
+    sizes = {"w1024": (1024, 4096), "w2048": (2048, 8192)}
+    want = [k for k in (args.sizes.split(",") if args.sizes else sizes) if k in sizes]
+    batch, plen, vocab = args.batch or 8, args.prompt_len, 32000
+    rng = np.random.default_rng(0)
+    out = []
+    for key in want:
+        W, ff = sizes[key]
+        H = W // 128
+        G = max(1, H // 4)
+        att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                              "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+        par = {"type": "parallel", "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                      "rot": {"base": 10000.0, "dims": 128}},
+                                             "right": {"heads": H, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16},
+                                             "left_scale": 0.7, "right_scale": 0.7}}
+        dense = {"kind": "dense", "ff": ff}
+        variants = {"mixed_loop": ([par, att, par, att], (1, 3, 2))}
+        if args.per_mixer:
+            variants["attention"] = ([att] * 4, None)
+            variants["parallel"] = ([par] * 4, None)
+        rec = {"size": key, "width": W, "ff": ff, "vocab": vocab, "batch": batch, "prompt_len": plen}
+        prompts = [rng.integers(0, vocab, plen).tolist() for _ in range(batch)]
+        P = InferenceParams(max_tokens=1 << 20, temperature=0.0)
+        ctx = plen + args.steps + args.warmup + 64
+
+        def measure(eng):
+            slots = [eng.seq_add(p, P) for p in prompts]
+            t_pre = []
+            for it in range(1 + max(1, args.ttft_runs)):
+                if it:
+                    for sl in slots:
+                        eng.seq_remove(sl)
+                    slots = [eng.seq_add(p, P) for p in prompts]
+                eng.step(slots, batch * plen)
+                t_pre.append(eng.status().last_step_ms)
+            for _ in range(args.warmup):
+                eng.decode(slots)
+            k0 = eng.status().kernel_launches
+            ms = 0.0
+            for _ in range(args.steps):
+                eng.decode(slots)
+                ms += eng.status().last_step_ms
+            launches = eng.status().kernel_launches - k0
+            for sl in slots:
+                eng.seq_remove(sl)
+            pre = min(t_pre[1:])
+            return {"prefill_ms": round(pre, 3), "prefill_tokens_per_s": round(batch * plen / pre * 1e3, 1),
+                    "decode_ms_per_step": round(ms / args.steps, 4), "decode_tokens_per_s": round(batch * args.steps / ms * 1e3, 1),
+                    "launches_per_decode_step": launches // max(1, args.steps)}
+        depths = set()
+        for vname, (layers, loop) in variants.items():
+            cfg = {"architecture": "Motolix", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": float(W) ** 0.5},
+                   "logit_scale": 0.5, "layers": [dict(json.loads(json.dumps(m)), mlp=dense) for m in layers]}
+            if loop:
+                cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+            spec = models.motolix_spec(cfg)
+            depths.add(len(spec.layer_runs()))
+            eng = Engine(WorkerConfig(None, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(batch * ctx + 63) // 64,
+                                      stack=spec, context_size=ctx, compute_dtype="bfloat16", flags=B_FLAG_NO_GRAPH if args.no_graph else 0))
+            for name, a in models.random_tensors(spec, seed=1).items():
+                eng.load_named(name, a)
+            eng.finalize()
+            rec["motolix_" + vname] = dict(measure(eng), layer_runs=len(spec.layer_runs()))
+            eng.close()
+        for depth in sorted(depths):
+            shape = ModelShape(vocab, W, depth, H, G, 128, ff, ctx)
+            eng = Engine(WorkerConfig(shape, max_batch=batch, max_step_tokens=batch * plen, page_size=64, kv_pages=(batch * ctx + 63) // 64 + batch))
+            eng.load_synthetic(1)
+            eng.finalize()
+            rec[f"llama_{depth}_layers"] = measure(eng)
+            eng.close()
+        out.append(rec)
+    line = {"metric": "motolix_vs_llama_equal_size", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random tokens)", "higher_is_better": True, "sizes": out}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -854,9 +940,9 @@ def main():
     ap.add_argument("--nccl-allreduce", action="store_true", help="TP: use NCCL instead of the fused peer-memory exchange (A/B)")
     ap.add_argument("--tp-exchange", choices=["auto", "oneshot", "twoshot", "ll", "wide"], default="auto",
                     help="TP: peer-memory exchange kernel (auto = ll, the flag-in-data row kernel, up to hidden 4096; wide, the same protocol on a (row, column block) grid, above)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn = the layer-list family beside Llama at equal size")
-    ap.add_argument("--sizes", default="", help="kidolorn: comma list out of w1024,w2048 (default both)")
-    ap.add_argument("--per-mixer", action="store_true", help="kidolorn: also four layers of each mixer alone")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "prefix", "kidolorn", "motolix"], help="serving = BASELINE configs[4]; prefix = TTFT with prefix KV reuse (row f2); kidolorn / motolix = that layer-list design beside Llama at equal size")
+    ap.add_argument("--sizes", default="", help="kidolorn, motolix: comma list out of w1024,w2048 (default both)")
+    ap.add_argument("--per-mixer", action="store_true", help="kidolorn, motolix: also four layers of each mixer alone")
     ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b = BASELINE configs[3] (TP=8, batch 32)")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--prefill-budget", type=int, default=0, help="serving: prompt tokens read per scheduler step (0 = library default)")
@@ -876,6 +962,8 @@ def main():
         return run_serving(args)
     if args.workload == "kidolorn":
         return run_kidolorn(args)
+    if args.workload == "motolix":
+        return run_motolix(args)
     return run_ours(args)
 
 

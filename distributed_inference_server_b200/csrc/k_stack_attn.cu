@@ -95,6 +95,8 @@ cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, i
 // denominator per pair).  Epilogue (whole history in one CTA) or merge kernel (slices): normalise, rotate the output back by
 // the query's position when values were rotated, scale, and store into the mixer's output row.
 constexpr int kAtTile = 32, kAtWarps = 8, kAtMaxSplit = 64;
+bool stack_attn_mma_ok(const StackAttn &c, bool f32);
+int stack_attn_mma_block_tokens(const StackAttn &c);
 
 struct AttnOut {
   void *out;          // [T][ld] in the compute type; head h at columns off + h * dv
@@ -115,7 +117,8 @@ __device__ __forceinline__ void attn_store(const AttnOut &o, const float *a, flo
   st_el<F32>(o.out, (long long)tok * o.ld + o.off + (long long)h * dv + j, v * o.scale);
 }
 
-int stack_attn_block_tokens(const StackAttn &c) {
+int stack_attn_block_tokens(const StackAttn &c, bool f32) {
+  if (stack_attn_mma_ok(c, f32)) return stack_attn_mma_block_tokens(c);
   const int R = c.H / c.G;
   int bq = std::max(1, 32 / R);
   while (bq > 1 && ((size_t)kAtTile * (c.d + c.dv + 2 + kAtWarps) + (size_t)bq * R * (c.d + c.dv + 2)) * 4 > 200 * 1024) bq >>= 1;
@@ -263,6 +266,250 @@ __global__ void stack_attn_merge_kernel(const float *part, int n_split, int T, i
   for (int j = threadIdx.x; j < dv; j += blockDim.x) attn_store<F32>(o, a, SIG ? 1.f : inv_den, tok, h, dv, j);
 }
 
+// ------------------------------------------------------------------------------------------------ attention on mma.sync
+// The bf16 compute type with dim a multiple of 8, vdim a multiple of 16, both at most 128, and at most 64 query heads per
+// key/value head.  A CTA of four warps owns up to 64 rows -- the (token, query head of the group) pairs of its query block,
+// 16 per warp -- and walks the history in tiles of 64 keys: K and V rows of the pages are copied with cp.async into two
+// shared-memory stages (the next tile is in flight while this one is used), S = Q K^T and O += P V run on m16n8k16 with fp32
+// accumulators, the weights in between are fp32 (online softmax per row, or the sigmoid form) and are rounded to bf16 only as
+// the operand of P V.  Slices and the epilogue are those of the kernel above.
+constexpr int kMmKeys = 64, kMmWarps = 4, kMmRows = 16 * kMmWarps;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {  // src_bytes 0: zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return (uint32_t)float_to_bf16_bits(lo) | ((uint32_t)float_to_bf16_bits(hi) << 16);
+}
+
+bool stack_attn_mma_ok(const StackAttn &c, bool f32) {
+  return !f32 && c.d % 8 == 0 && c.dv % 16 == 0 && c.d <= 128 && c.dv <= 128 && c.H / c.G <= kMmRows;
+}
+int stack_attn_mma_block_tokens(const StackAttn &c) { return std::max(1, kMmRows / (c.H / c.G)); }
+
+template <int DMAX, bool SIG>
+__global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const float *__restrict__ qf, const uint16_t *__restrict__ kpool,
+                                                                       const uint16_t *__restrict__ vpool, const float *temp,
+                                                                       const float *pb, StackAttn c, StackSpans sp, const int *qb_tok0,
+                                                                       const int *qb_len, const int *page_table, int max_pages,
+                                                                       int page_size, AttnOut o, int keys_per_split, float *part) {
+  constexpr int PITCH = DMAX + 8;  // elements per shared row: 16-byte rows land in distinct bank groups
+  extern __shared__ __align__(16) uint16_t smem[];
+  uint16_t *Ks = smem;                                  // [2][64][PITCH]
+  uint16_t *Vs = smem + 2 * kMmKeys * PITCH;            // [2][64][PITCH]
+  const int d = c.d, dv = c.dv, R = c.H / c.G, kvh = blockIdx.y;
+  const int tok0 = qb_tok0[blockIdx.x], nq = qb_len[blockIdx.x], rows = nq * R;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, qd = lane & 3;
+  const int slot = sp.slot[tok0], pos_first = sp.pos[tok0], last_pos = pos_first + nq - 1;
+  const int *pt = page_table + (long long)slot * max_pages;
+  const int k_begin = part ? (int)blockIdx.z * keys_per_split : 0;
+  const int k_end = part ? min(last_pos + 1, k_begin + keys_per_split) : last_pos + 1;
+  const int nk16 = (d + 15) >> 4, nv8 = dv >> 3, dc = d >> 3, vc = dv >> 3;  // k-steps of Q K^T, n-tiles of P V, 16-byte chunks per row
+  // columns d .. 16 nk16 of the K stages are read by the last k-step: zero them once (cp.async never touches them)
+  if (d & 15)
+    for (int i = threadIdx.x; i < 2 * kMmKeys * 8; i += blockDim.x) Ks[(i >> 3) * PITCH + d + (i & 7)] = 0;
+  // ---- this thread's rows: r0 = 16 warp + gid and r0 + 8
+  int r_tok[2], r_head[2], r_pos[2];
+  bool r_ok[2];
+  uint32_t qa[DMAX / 16][4];
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    const int r = warp * 16 + gid + e * 8;
+    r_ok[e] = r < rows;
+    r_tok[e] = tok0 + (r_ok[e] ? r / R : 0);
+    r_head[e] = kvh * R + (r_ok[e] ? r % R : 0);
+    r_pos[e] = r_ok[e] ? pos_first + r / R : -1;
+  }
+#pragma unroll
+  for (int ks = 0; ks < DMAX / 16; ks++) {
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const float *qr = qf + ((long long)r_tok[e] * c.H + r_head[e]) * d;
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) {
+        const int col = ks * 16 + hf * 8 + qd * 2;
+        float x0 = 0.f, x1 = 0.f;
+        if (r_ok[e] && ks < nk16) {
+          if (col < d) x0 = qr[col];
+          if (col + 1 < d) x1 = qr[col + 1];
+        }
+        qa[ks][hf * 2 + e] = pack_bf16(x0, x1);
+      }
+    }
+  }
+  float oacc[DMAX / 8][4];
+#pragma unroll
+  for (int j = 0; j < DMAX / 8; j++) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  float tmp_h[2] = {1.f, 1.f}, pb_h[2] = {0.f, 0.f};
+  if (SIG) {
+#pragma unroll
+    for (int e = 0; e < 2; e++) { tmp_h[e] = temp[r_head[e]] * c.scale; pb_h[e] = pb[r_head[e]]; }
+  }
+  const bool warp_live = warp * 16 < rows;
+  const int warp_last_pos = pos_first + min(rows - 1, warp * 16 + 15) / R;
+  const long long krow = (long long)c.G * d, vrow = (long long)c.G * dv;
+  const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
+  auto load_tile = [&](int k0, int stage) {
+    const int nk = min(kMmKeys, k_end - k0);
+    for (int i = threadIdx.x; i < kMmKeys * dc; i += blockDim.x) {
+      const int kk = i / dc, ch = i - kk * dc, kp = k0 + kk;
+      const bool ok = kk < nk;
+      const long long prow = ok ? (long long)pt[kp / page_size] * page_size + kp % page_size : 0;
+      cp_async16(ks_base + (uint32_t)(((stage * kMmKeys + kk) * PITCH + ch * 8) * 2), kpool + prow * krow + (long long)kvh * d + ch * 8, ok ? 16 : 0);
+    }
+    for (int i = threadIdx.x; i < kMmKeys * vc; i += blockDim.x) {
+      const int kk = i / vc, ch = i - kk * vc, kp = k0 + kk;
+      const bool ok = kk < nk;
+      const long long prow = ok ? (long long)pt[kp / page_size] * page_size + kp % page_size : 0;
+      cp_async16(vs_base + (uint32_t)(((stage * kMmKeys + kk) * PITCH + ch * 8) * 2), vpool + prow * vrow + (long long)kvh * dv + ch * 8, ok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + kMmKeys - 1) / kMmKeys : 0;
+  if (n_tiles > 0) load_tile(k_begin, 0);
+  for (int it = 0; it < n_tiles; it++) {
+    const int k0 = k_begin + it * kMmKeys, stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_tile(k0 + kMmKeys, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp_live && k0 <= warp_last_pos) {
+      const uint16_t *Kt = Ks + stage * kMmKeys * PITCH;
+      float sacc[kMmKeys / 8][4];
+#pragma unroll
+      for (int j = 0; j < kMmKeys / 8; j++) {
+        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+        const uint16_t *kr = Kt + (j * 8 + gid) * PITCH + qd * 2;
+#pragma unroll
+        for (int ks = 0; ks < DMAX / 16; ks++) {
+          if (ks < nk16) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kr + ks * 16), b1 = *reinterpret_cast<const uint32_t *>(kr + ks * 16 + 8);
+            mma_bf16_16816(sacc[j], qa[ks], b0, b1);
+          }
+        }
+      }
+      // ---- weights, fp32
+      float mnew[2] = {mrow[0], mrow[1]};
+#pragma unroll
+      for (int j = 0; j < kMmKeys / 8; j++)
+#pragma unroll
+        for (int q4 = 0; q4 < 4; q4++) {
+          const int e = q4 >> 1, kp = k0 + j * 8 + qd * 2 + (q4 & 1);
+          const bool vis = kp <= r_pos[e] && kp < k_end;
+          float sv = sacc[j][q4];
+          if (SIG) sv = vis ? 1.f / (1.f + __expf(-(sv * tmp_h[e] + pb_h[e]))) : 0.f;
+          else { sv = vis ? sv * c.scale : -INFINITY; mnew[e] = fmaxf(mnew[e], sv); }
+          sacc[j][q4] = sv;
+        }
+      if (!SIG) {
+        float corr[2];
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          mnew[e] = fmaxf(mnew[e], __shfl_xor_sync(0xffffffffu, mnew[e], 1));
+          mnew[e] = fmaxf(mnew[e], __shfl_xor_sync(0xffffffffu, mnew[e], 2));
+          corr[e] = mrow[e] == -INFINITY ? 0.f : __expf(mrow[e] - mnew[e]);
+          mrow[e] = mnew[e];
+          lrow[e] *= corr[e];
+        }
+#pragma unroll
+        for (int j = 0; j < kMmKeys / 8; j++)
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) {
+            const int e = q4 >> 1;
+            const float pv = sacc[j][q4] == -INFINITY ? 0.f : __expf(sacc[j][q4] - mnew[e]);
+            sacc[j][q4] = pv;
+            lrow[e] += pv;
+          }
+#pragma unroll
+        for (int j = 0; j < DMAX / 8; j++) { oacc[j][0] *= corr[0]; oacc[j][1] *= corr[0]; oacc[j][2] *= corr[1]; oacc[j][3] *= corr[1]; }
+      }
+      // ---- O += P V
+      const uint32_t vt = vs_base + (uint32_t)(stage * kMmKeys * PITCH * 2);
+#pragma unroll
+      for (int kk = 0; kk < kMmKeys / 16; kk++) {
+        uint32_t pa[4];
+        pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
+        pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
+        pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+        pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+#pragma unroll
+        for (int j = 0; j < DMAX / 8; j += 2) {
+          if (j < nv8) {
+            // lanes 0-15: keys 16 kk + lane of columns 8 j; lanes 16-31: the same keys of columns 8 (j + 1)
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_trans(vt + (uint32_t)(((kk * 16 + (lane & 15)) * PITCH + (j + (lane >> 4)) * 8) * 2), b0, b1, b2, b3);
+            mma_bf16_16816(oacc[j], pa, b0, b1);
+            mma_bf16_16816(oacc[j + 1], pa, b2, b3);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (!SIG) {
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      lrow[e] += __shfl_xor_sync(0xffffffffu, lrow[e], 1);
+      lrow[e] += __shfl_xor_sync(0xffffffffu, lrow[e], 2);
+    }
+  }
+  // ---- results: thread holds, for row e, columns 8 j + 2 qd + {0, 1} of every n-tile j
+  if (!part && o.vrot) {
+    // rotation back by the query's position pairs column m with m + dv/2: the warp's 16 x dv tile goes through shared memory
+    // (every key tile has been consumed; a warp reads only the rows it wrote)
+    float *ot = reinterpret_cast<float *>(smem) + (size_t)warp * 16 * (dv + 1);
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+#pragma unroll
+      for (int j = 0; j < DMAX / 8; j++)
+        if (j < nv8) { ot[(gid + e * 8) * (dv + 1) + j * 8 + qd * 2] = oacc[j][e * 2]; ot[(gid + e * 8) * (dv + 1) + j * 8 + qd * 2 + 1] = oacc[j][e * 2 + 1]; }
+      if (qd == 0) ot[(gid + e * 8) * (dv + 1) + dv] = SIG ? o.scale : o.scale / lrow[e];
+    }
+    __syncwarp();
+    const int hf = dv >> 1;
+    for (int i = lane; i < 16 * hf; i += 32) {
+      const int rr = i / hf, m = i - rr * hf, r = warp * 16 + rr;
+      if (r >= rows) continue;
+      const int tok = tok0 + r / R, head = kvh * R + r % R;
+      const float *cs = o.vrot + (long long)tok * dv, *sn = cs + hf;
+      const float u = ot[rr * (dv + 1) + m], w = ot[rr * (dv + 1) + m + hf], inv = ot[rr * (dv + 1) + dv];
+      uint16_t *orow = reinterpret_cast<uint16_t *>(o.out) + (long long)tok * o.ld + o.off + (long long)head * dv;
+      orow[m] = float_to_bf16_bits((u * cs[m] + w * sn[m]) * inv);
+      orow[m + hf] = float_to_bf16_bits((w * cs[m] - u * sn[m]) * inv);
+    }
+    return;
+  }
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    if (!r_ok[e]) continue;
+    if (part) {
+      float *rec = part + (((long long)blockIdx.z * sp.T + r_tok[e]) * c.H + r_head[e]) * (dv + 2);
+#pragma unroll
+      for (int j = 0; j < DMAX / 8; j++)
+        if (j < nv8) { rec[j * 8 + qd * 2] = oacc[j][e * 2]; rec[j * 8 + qd * 2 + 1] = oacc[j][e * 2 + 1]; }
+      if (qd == 0) { rec[dv] = SIG ? 0.f : mrow[e]; rec[dv + 1] = lrow[e]; }
+      continue;
+    }
+    const float inv = SIG ? o.scale : o.scale / lrow[e];
+    uint16_t *orow = reinterpret_cast<uint16_t *>(o.out) + (long long)r_tok[e] * o.ld + o.off + (long long)r_head[e] * dv;
+#pragma unroll
+    for (int j = 0; j < DMAX / 8; j++)
+      if (j < nv8) *reinterpret_cast<uint32_t *>(orow + j * 8 + qd * 2) = pack_bf16(oacc[j][e * 2] * inv, oacc[j][e * 2 + 1] * inv);
+  }
+}
+
 cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vpool, bool f32, const float *temp, const float *pb,
                               const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, int bq,
                               const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
@@ -282,6 +529,34 @@ cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vp
   }));
   const AttnOut o{out, ld_out, out_off, out_scale, (c.flags & DIS_ATTN_ROT_V) ? vrot : nullptr};
   const dim3 grid(n_qb, c.G, n_split);
+  static int use_mma = -1;
+  if (use_mma < 0) { const char *e = getenv("DIS_STACK_ATTN_MMA"); use_mma = (e && atoi(e) == 0) ? 0 : 1; }
+  // the output's 4-byte stores want even columns; bq is the block size the pass was planned with
+  if (use_mma && stack_attn_mma_ok(c, f32) && bq <= stack_attn_mma_block_tokens(c) && ld_out % 2 == 0 && out_off % 2 == 0) {
+    static DeviceOnce once_mma;
+    DIS_CUDA_TRY(once_mma.run([&] {
+      cudaError_t e = cudaFuncSetAttribute(stack_attn_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_attn_mma_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_attn_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      return e != cudaSuccess ? e : cudaFuncSetAttribute(stack_attn_mma_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    }));
+    const bool small = c.d <= 64 && c.dv <= 64;
+    const size_t shm = (size_t)4 * kMmKeys * ((small ? 64 : 128) + 8) * sizeof(uint16_t);
+    const uint16_t *kp = reinterpret_cast<const uint16_t *>(kpool), *vp = reinterpret_cast<const uint16_t *>(vpool);
+#define DIS_ATTN_MMA(D, S) \
+  stack_attn_mma_kernel<D, S><<<grid, kMmWarps * 32, shm, st>>>(qf, kp, vp, temp, pb, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, o, keys_per_split, part)
+    if (small && sig) DIS_ATTN_MMA(64, true);
+    else if (small) DIS_ATTN_MMA(64, false);
+    else if (sig) DIS_ATTN_MMA(128, true);
+    else DIS_ATTN_MMA(128, false);
+#undef DIS_ATTN_MMA
+    if (part) {
+      const size_t msh = (size_t)(c.dv + n_split) * sizeof(float);
+      if (sig) stack_attn_merge_kernel<false, true><<<sp.T * c.H, 64, msh, st>>>(part, n_split, sp.T, c.H, c.dv, o);
+      else stack_attn_merge_kernel<false, false><<<sp.T * c.H, 64, msh, st>>>(part, n_split, sp.T, c.H, c.dv, o);
+    }
+    return cudaGetLastError();
+  }
   const int th = kAtWarps * 32;
 #define DIS_ATTN_LAUNCH(F, S) \
   stack_attn_kernel<F, S><<<grid, th, sh, st>>>(qf, kpool, vpool, temp, pb, c, sp, qb_tok0, qb_len, page_table, max_pages, page_size, o, keys_per_split, part)

@@ -325,7 +325,10 @@ cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_o
                              cudaStream_t st) {
   const LightCols col{q_off, k_off, v_off};
   const float qscale = 1.f / sqrtf((float)d);
+  // rows of S per warp (RI) and columns per lane (RJ) chosen so that all eight warps own rows: d <= 8 RI, dv <= 32 RJ
+  if (d <= 32 && dv <= 64) return lightning_reg<4, 2, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 64 && dv <= 64) return lightning_reg<8, 2, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
+  if (d <= 64 && dv <= 128) return lightning_reg<8, 4, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 128 && dv <= 128) return lightning_reg<16, 4, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   return cudaErrorInvalidValue;
 }

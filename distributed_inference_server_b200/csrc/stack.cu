@@ -148,7 +148,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
         return fail(DIS_ERR_INVALID_ARGUMENT, at + "rotary scaling needs original > 0 and 0 < low != high");
       const int H = lc.heads, G = lc.kv_heads, d = lc.dim, dv = lc.vdim;
       StackAttn sa{H, G, d, dv, lc.rot_dims, lc.attn_flags, lc.scale, sc->norm_eps};
-      const int bq = stack_attn_block_tokens(sa);
+      const int bq = stack_attn_block_tokens(sa, sc->compute_dtype == DIS_F32);
       if (((size_t)32 * (d + dv + 10) + (size_t)(H / G) * (d + dv + 2)) * 4 > 200 * 1024) return fail(DIS_ERR_INVALID_ARGUMENT, at + "dim + vdim does not fit shared memory");
       stack_abq = stack_abq ? std::min(stack_abq, bq) : bq;
       stack_att_heads = std::max(stack_att_heads, H);

@@ -104,7 +104,9 @@ cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, i
 // query blocks hold at most stack_attn_block_tokens() tokens of one span; n_split > 1: slices of keys_per_split keys (a multiple
 // of 32), records of dv + 2 floats per (slice, token, head) in `part`, merged by a second kernel.  The result, times out_scale
 // and rotated back when values were rotated, lands in out [T][ld_out] (compute type) at columns out_off + h * dv.
-int stack_attn_block_tokens(const StackAttn &c);
+// bf16 with dim % 8 == 0, vdim % 16 == 0, both <= 128 and at most 64 query heads per key/value head: the mma.sync kernel (blocks
+// of 64 (token, head) rows); otherwise the fp32-arithmetic kernel
+int stack_attn_block_tokens(const StackAttn &c, bool f32);
 cudaError_t launch_stack_attn(const float *qf, const void *kpool, const void *vpool, bool f32, const float *temp, const float *pb,
                               const StackAttn &c, const StackSpans &sp, const int *qb_tok0, const int *qb_len, int n_qb, int bq,
                               const int *page_table, int max_pages, int page_size, void *out, long long ld_out, int out_off,
