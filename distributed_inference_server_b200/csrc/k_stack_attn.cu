@@ -24,18 +24,21 @@ __global__ void __launch_bounds__(128) stack_attn_prep_kernel(const float *proj,
   const int half = c.rot_dims >> 1, vhalf = c.dv >> 1;
   const bool rot_v = (c.flags & DIS_ATTN_ROT_V) != 0;
   float *cs = tab, *sn = tab + half, *vcs = sn + half, *vsn = vcs + vhalf;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    double s_, c_;
-    sincos((double)pos * freq[i], &s_, &c_);
-    cs[i] = (float)c_; sn[i] = (float)s_;
-  }
+  // the angle pos * f is formed and brought into [-pi, pi] in double (position 100000 is then as exact as position 5); sine and
+  // cosine of the reduced angle are float
+  auto angle = [](int p, double f, float *sn_out, float *cs_out) {
+    const double a = (double)p * f;
+    const double r = a - 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+    sincosf((float)r, sn_out, cs_out);
+  };
+  for (int i = threadIdx.x; i < half; i += blockDim.x) angle(pos, freq[i], &sn[i], &cs[i]);
   if (rot_v)
     for (int i = threadIdx.x; i < vhalf; i += blockDim.x) {
-      double s_, c_;
-      sincos((double)pos * vfreq[i], &s_, &c_);
-      vcs[i] = (float)c_; vsn[i] = (float)s_;
-      vrot[(long long)t * c.dv + i] = (float)c_;
-      vrot[(long long)t * c.dv + vhalf + i] = (float)s_;
+      float s_, c_;
+      angle(pos, vfreq[i], &s_, &c_);
+      vcs[i] = c_; vsn[i] = s_;
+      vrot[(long long)t * c.dv + i] = c_;
+      vrot[(long long)t * c.dv + vhalf + i] = s_;
     }
   const int nq = c.H * c.d, nk = c.G * c.d;
   const float *qb = bias, *kb = bias ? bias + nq : nullptr;
@@ -274,11 +277,15 @@ __global__ void stack_attn_merge_kernel(const float *part, int n_split, int T, i
 // accumulators, the weights in between are fp32 (online softmax per row, or the sigmoid form) and are rounded to bf16 only as
 // the operand of P V.  Slices and the epilogue are those of the kernel above.
 constexpr int kMmKeys = 64, kMmWarps = 4, kMmRows = 16 * kMmWarps;
+constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -296,7 +303,7 @@ bool stack_attn_mma_ok(const StackAttn &c, bool f32) {
 int stack_attn_mma_block_tokens(const StackAttn &c) { return std::max(1, kMmRows / (c.H / c.G)); }
 
 template <int DMAX, bool SIG>
-__global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const float *__restrict__ qf, const uint16_t *__restrict__ kpool,
+__global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const float *__restrict__ qf, const uint16_t *__restrict__ kpool,
                                                                        const uint16_t *__restrict__ vpool, const float *temp,
                                                                        const float *pb, StackAttn c, StackSpans sp, const int *qb_tok0,
                                                                        const int *qb_len, const int *page_table, int max_pages,
@@ -306,7 +313,10 @@ __global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const flo
   uint16_t *Ks = smem;                                  // [2][64][PITCH]
   uint16_t *Vs = smem + 2 * kMmKeys * PITCH;            // [2][64][PITCH]
   const int d = c.d, dv = c.dv, R = c.H / c.G, kvh = blockIdx.y;
-  const int tok0 = qb_tok0[blockIdx.x], nq = qb_len[blockIdx.x], rows = nq * R;
+  // the blocks of a span come in ascending position, and the later ones walk a longer history: taking the grid backwards starts
+  // the long ones first, so the last CTAs to start are short
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int tok0 = qb_tok0[qb], nq = qb_len[qb], rows = nq * R;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, qd = lane & 3;
   const int slot = sp.slot[tok0], pos_first = sp.pos[tok0], last_pos = pos_first + nq - 1;
   const int *pt = page_table + (long long)slot * max_pages;
@@ -352,26 +362,30 @@ __global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const flo
   float tmp_h[2] = {1.f, 1.f}, pb_h[2] = {0.f, 0.f};
   if (SIG) {
 #pragma unroll
-    for (int e = 0; e < 2; e++) { tmp_h[e] = temp[r_head[e]] * c.scale; pb_h[e] = pb[r_head[e]]; }
+    for (int e = 0; e < 2; e++) { tmp_h[e] = temp[r_head[e]] * c.scale * kLog2e; pb_h[e] = pb[r_head[e]] * kLog2e; }
   }
+  const float scale2 = c.scale * kLog2e;
   const bool warp_live = warp * 16 < rows;
   const int warp_last_pos = pos_first + min(rows - 1, warp * 16 + 15) / R;
   const long long krow = (long long)c.G * d, vrow = (long long)c.G * dv;
   const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
+  // two threads per key row: one page-table read per thread and tile, then the row's 16-byte chunks alternate between the two
+  const int ld_row = threadIdx.x >> 1, ld_part = threadIdx.x & 1;
+  const int pshift = 31 - __clz(page_size);  // page_size is a power of two
+  // the page of this thread's row is read one tile ahead of the copy that needs it
+  auto page_of = [&](int k0) { const int kp = k0 + ld_row; return kp < k_end ? pt[kp >> pshift] : 0; };
+  int page_next = page_of(k_begin);
   auto load_tile = [&](int k0, int stage) {
-    const int nk = min(kMmKeys, k_end - k0);
-    for (int i = threadIdx.x; i < kMmKeys * dc; i += blockDim.x) {
-      const int kk = i / dc, ch = i - kk * dc, kp = k0 + kk;
-      const bool ok = kk < nk;
-      const long long prow = ok ? (long long)pt[kp / page_size] * page_size + kp % page_size : 0;
-      cp_async16(ks_base + (uint32_t)(((stage * kMmKeys + kk) * PITCH + ch * 8) * 2), kpool + prow * krow + (long long)kvh * d + ch * 8, ok ? 16 : 0);
-    }
-    for (int i = threadIdx.x; i < kMmKeys * vc; i += blockDim.x) {
-      const int kk = i / vc, ch = i - kk * vc, kp = k0 + kk;
-      const bool ok = kk < nk;
-      const long long prow = ok ? (long long)pt[kp / page_size] * page_size + kp % page_size : 0;
-      cp_async16(vs_base + (uint32_t)(((stage * kMmKeys + kk) * PITCH + ch * 8) * 2), vpool + prow * vrow + (long long)kvh * dv + ch * 8, ok ? 16 : 0);
-    }
+    const int kp = k0 + ld_row;
+    const bool ok = kp < k_end;
+    const long long prow = ok ? (long long)page_next * page_size + (kp & (page_size - 1)) : 0;
+    page_next = page_of(k0 + kMmKeys);
+    const uint16_t *ksrc = kpool + prow * krow + (long long)kvh * d, *vsrc = vpool + prow * vrow + (long long)kvh * dv;
+    const uint32_t kdst = ks_base + (uint32_t)(((stage * kMmKeys + ld_row) * PITCH) * 2), vdst = vs_base + (uint32_t)(((stage * kMmKeys + ld_row) * PITCH) * 2);
+#pragma unroll 4
+    for (int ch = ld_part; ch < dc; ch += 2) cp_async16(kdst + ch * 16, ksrc + ch * 8, ok ? 16 : 0);
+#pragma unroll 4
+    for (int ch = ld_part; ch < vc; ch += 2) cp_async16(vdst + ch * 16, vsrc + ch * 8, ok ? 16 : 0);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + kMmKeys - 1) / kMmKeys : 0;
@@ -387,30 +401,41 @@ __global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const flo
     __syncthreads();
     if (warp_live && k0 <= warp_last_pos) {
       const uint16_t *Kt = Ks + stage * kMmKeys * PITCH;
+      // S = Q K^T: k-steps outside, key tiles inside, so that consecutive products go to different accumulators; one ldmatrix
+      // brings the fragments of two key tiles (lane l: matrix l / 8 = (tile, column half), row l % 8)
+      const uint32_t kt = ks_base + (uint32_t)(stage * kMmKeys * PITCH * 2);
       float sacc[kMmKeys / 8][4];
 #pragma unroll
-      for (int j = 0; j < kMmKeys / 8; j++) {
-        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
-        const uint16_t *kr = Kt + (j * 8 + gid) * PITCH + qd * 2;
+      for (int j = 0; j < kMmKeys / 8; j++) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
 #pragma unroll
-        for (int ks = 0; ks < DMAX / 16; ks++) {
-          if (ks < nk16) {
-            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kr + ks * 16), b1 = *reinterpret_cast<const uint32_t *>(kr + ks * 16 + 8);
+      for (int ks = 0; ks < DMAX / 16; ks++) {
+        if (ks < nk16) {
+#pragma unroll
+          for (int j = 0; j < kMmKeys / 8; j += 2) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(kt + (uint32_t)((((j + (lane >> 4)) * 8 + (lane & 7)) * PITCH + ks * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1, b2, b3);
             mma_bf16_16816(sacc[j], qa[ks], b0, b1);
+            mma_bf16_16816(sacc[j + 1], qa[ks], b2, b3);
           }
         }
       }
-      // ---- weights, fp32
+      // ---- weights, fp32.  Scores are carried in units of log 2 (the factor 1 / ln 2 is folded into the scale), so every
+      // exponential is one ex2.  Only a tile that reaches past a row's position or the slice's end needs the mask.
+      const bool masked = k0 + kMmKeys - 1 > pos_first + (warp * 16) / R || k0 + kMmKeys > k_end;
       float mnew[2] = {mrow[0], mrow[1]};
 #pragma unroll
       for (int j = 0; j < kMmKeys / 8; j++)
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
-          const int e = q4 >> 1, kp = k0 + j * 8 + qd * 2 + (q4 & 1);
-          const bool vis = kp <= r_pos[e] && kp < k_end;
+          const int e = q4 >> 1;
+          bool vis = true;
+          if (masked) { const int kp = k0 + j * 8 + qd * 2 + (q4 & 1); vis = kp <= r_pos[e] && kp < k_end; }
           float sv = sacc[j][q4];
-          if (SIG) sv = vis ? 1.f / (1.f + __expf(-(sv * tmp_h[e] + pb_h[e]))) : 0.f;
-          else { sv = vis ? sv * c.scale : -INFINITY; mnew[e] = fmaxf(mnew[e], sv); }
+          if (SIG) {
+            float rc;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.f + exp2f(-fmaf(sv, tmp_h[e], pb_h[e]))));
+            sv = vis ? rc : 0.f;
+          } else { sv = vis ? sv * scale2 : -INFINITY; mnew[e] = fmaxf(mnew[e], sv); }
           sacc[j][q4] = sv;
         }
       if (!SIG) {
@@ -419,16 +444,17 @@ __global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const flo
         for (int e = 0; e < 2; e++) {
           mnew[e] = fmaxf(mnew[e], __shfl_xor_sync(0xffffffffu, mnew[e], 1));
           mnew[e] = fmaxf(mnew[e], __shfl_xor_sync(0xffffffffu, mnew[e], 2));
-          corr[e] = mrow[e] == -INFINITY ? 0.f : __expf(mrow[e] - mnew[e]);
+          corr[e] = mrow[e] == -INFINITY ? 0.f : exp2f(mrow[e] - mnew[e]);
           mrow[e] = mnew[e];
           lrow[e] *= corr[e];
         }
+        const float msub[2] = {mnew[0] == -INFINITY ? 0.f : mnew[0], mnew[1] == -INFINITY ? 0.f : mnew[1]};  // a row with nothing visible yet
 #pragma unroll
         for (int j = 0; j < kMmKeys / 8; j++)
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) {
             const int e = q4 >> 1;
-            const float pv = sacc[j][q4] == -INFINITY ? 0.f : __expf(sacc[j][q4] - mnew[e]);
+            const float pv = exp2f(sacc[j][q4] - msub[e]);  // 2^(-inf) = 0 for the masked
             sacc[j][q4] = pv;
             lrow[e] += pv;
           }
@@ -499,7 +525,7 @@ __global__ void __launch_bounds__(kMmWarps * 32) stack_attn_mma_kernel(const flo
 #pragma unroll
       for (int j = 0; j < DMAX / 8; j++)
         if (j < nv8) { rec[j * 8 + qd * 2] = oacc[j][e * 2]; rec[j * 8 + qd * 2 + 1] = oacc[j][e * 2 + 1]; }
-      if (qd == 0) { rec[dv] = SIG ? 0.f : mrow[e]; rec[dv + 1] = lrow[e]; }
+      if (qd == 0) { rec[dv] = SIG ? 0.f : mrow[e] * kLn2; rec[dv + 1] = lrow[e]; }  // the maximum back in natural units
       continue;
     }
     const float inv = SIG ? o.scale : o.scale / lrow[e];
