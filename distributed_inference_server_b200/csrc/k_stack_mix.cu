@@ -11,8 +11,13 @@ __device__ __forceinline__ float silu_(float v) { return v / (1.f + expf(-v)); }
 // One CTA per (span, head).  S [d][dv] lives in shared memory for the whole span; per token: S = a S + k v^T, o = S^T q.
 // Warp w owns rows i = w, w + nw, ...; lanes own columns.  The partial o of every warp goes through shared memory and is added
 // in warp order, so the sum's order is fixed.  A span that starts at position 0 starts from S = 0 (the slot is not read).
-__global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj, long long ld, const float *decay, float *state,
-                                                              StackSpans sp, float *o, int H, int d, int dv) {
+// GATE false: one decay per head, q, k, v through SiLU.  GATE true: the decay is a vector per token (dec [T][H*d], one factor per
+// row of S), q is multiplied by qscale, no activation.
+struct LightCols { int q, k, v; };  // first column of head 0's q, k, v in a row of proj
+template <bool GATE>
+__global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj, long long ld, LightCols col, const float *decay,
+                                                              const float *dec, float qscale, float *state, StackSpans sp, float *o, int H,
+                                                              int d, int dv) {
   extern __shared__ float shm[];
   const int s = blockIdx.x, h = blockIdx.y;
   const int tok0 = sp.sp_tok0[s], len = sp.sp_len[s], pos0 = sp.sp_pos0[s], slot = sp.sp_slot[s];
@@ -22,23 +27,29 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
   float *ks = qs + d;             // [d]
   float *vs = ks + d;             // [dv]
   float *part = vs + dv;          // [nw][dv]
+  float *as = part + (size_t)nw * dv;  // [d] (GATE)
   float *st = state + ((long long)slot * H + h) * d * dv;
-  const float a = decay[h];
+  const float a = GATE ? 1.f : decay[h];
   for (int i = threadIdx.x; i < d * dv; i += blockDim.x) S[i] = pos0 > 0 ? st[i] : 0.f;
   for (int t = 0; t < len; t++) {
     const float *row = proj + (long long)(tok0 + t) * ld;
     __syncthreads();
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      qs[i] = silu_(row[(long long)h * d + i]);
-      ks[i] = silu_(row[(long long)H * d + (long long)h * d + i]);
+      const float qv = row[col.q + (long long)h * d + i], kv = row[col.k + (long long)h * d + i];
+      qs[i] = GATE ? qv * qscale : silu_(qv);
+      ks[i] = GATE ? kv : silu_(kv);
+      if (GATE) as[i] = dec[(long long)(tok0 + t) * H * d + (long long)h * d + i];
     }
-    for (int j = threadIdx.x; j < dv; j += blockDim.x) vs[j] = silu_(row[(long long)2 * H * d + (long long)h * dv + j]);
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+      const float vv = row[col.v + (long long)h * dv + j];
+      vs[j] = GATE ? vv : silu_(vv);
+    }
     __syncthreads();
     for (int j = l; j < dv; j += 32) {
       const float vj = vs[j];
       float acc = 0.f;
       for (int i = w; i < d; i += nw) {
-        const float sv = fmaf(a, S[(size_t)i * dv + j], ks[i] * vj);
+        const float sv = fmaf(GATE ? as[i] : a, S[(size_t)i * dv + j], ks[i] * vj);
         S[(size_t)i * dv + j] = sv;
         acc = fmaf(sv, qs[i], acc);
       }
@@ -68,7 +79,6 @@ __global__ void __launch_bounds__(256) stack_lightning_kernel(const float *proj,
 // S_in(c+1) = A_c S_in(c) + contribution(c), leaving S_in(c) in `seg`;
 // MODE 2: the segment's outputs, starting from S_in(c).
 constexpr int kLightTok = 8, kLightSeg = 64;
-struct LightCols { int q, k, v; };  // first column of head 0's q, k, v in a row of proj
 template <int RI, int RJ, int MODE, bool GATE>
 __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float *__restrict__ proj, long long ld, LightCols col,
                                                                      const float *decay, const float *__restrict__ dec, float qscale,
@@ -288,8 +298,8 @@ cudaError_t launch_stack_lightning(const float *proj, long long ld, const float 
   const size_t sh = ((size_t)d * dv + 2 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
   if (sh > 220 * 1024) return cudaErrorInvalidValue;
   static DeviceOnce once;
-  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
-  stack_lightning_kernel<<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, decay, state, sp, o, H, d, dv);
+  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
+  stack_lightning_kernel<false><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, col, decay, nullptr, 1.f, state, sp, o, H, d, dv);
   return cudaGetLastError();
 }
 
@@ -330,7 +340,14 @@ cudaError_t launch_stack_gla(const float *proj, long long ld, int q_off, int k_o
   if (d <= 64 && dv <= 64) return lightning_reg<8, 2, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 64 && dv <= 128) return lightning_reg<8, 4, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
   if (d <= 128 && dv <= 128) return lightning_reg<16, 4, true>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv, seg, seg_a, max_len, st);
-  return cudaErrorInvalidValue;
+  // larger heads: the state of one head in shared memory, one CTA per (span, head)
+  const int threads = 256;
+  const size_t sh = ((size_t)d * dv + 3 * d + dv + (size_t)(threads / 32) * dv) * sizeof(float);
+  if (sh > 220 * 1024) return cudaErrorInvalidValue;
+  static DeviceOnce once;
+  DIS_CUDA_TRY(once.run([&] { return cudaFuncSetAttribute(stack_lightning_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); }));
+  stack_lightning_kernel<true><<<dim3(sp.n_spans, H), threads, sh, st>>>(proj, ld, col, nullptr, dec, qscale, state, sp, o, H, d, dv);
+  return cudaGetLastError();
 }
 
 // out[t][off + h*dv + j] = scale * o[t][h][j] / rms(o[t][h]) * w[j] * silu(gate[t][h*dv + j]): the norm runs over one head's dv

@@ -100,6 +100,39 @@ def test_long_recurrent_spans_run_as_segments_with_a_carry(heads, dim, vdim):
     assert U.rel_err(U.run_portions(cfg, W, t, [7, 200, 65, 20]), want) < F32_TOL
 
 
+TENSOR_CORE_SHAPES = {
+    # bfloat16 with dim % 8 == 0 and vdim % 16 == 0 runs attention on the tensor cores; the float32 run of the same model takes the
+    # fp32-arithmetic kernel
+    "sigmoid_16": [(U.attention(heads=4, kv_heads=2, dim=16, rot_dims=8), None)],
+    "sigmoid_112_three_per_group": [(U.attention(heads=3, kv_heads=1, dim=112, rot_dims=112), None)],
+    "softmax_dim8_vdim16": [(U.parallel(heads=4, kv_heads=4, dim=8, vdim=16, rot_dims=8, right_scale=0.2), None)],
+    "softmax_dim24_vdim32_six_per_group": [(U.parallel(heads=6, kv_heads=1, dim=24, vdim=32, rot_dims=12, right_scale=0.2), None)],
+    "softmax_dim72_vdim80": [(U.parallel(heads=2, kv_heads=1, dim=72, vdim=80, rot_dims=72, right_scale=0.2), None)],
+    "softmax_dim128_vdim128_seventy_per_group": [(U.parallel(heads=70, kv_heads=1, dim=128, vdim=128, rot_dims=64, right_scale=0.2), None)],
+}
+
+
+@pytest.mark.parametrize("name", sorted(TENSOR_CORE_SHAPES))
+def test_attention_on_tensor_cores(name):
+    """Whole prompt, ragged portions (blocks that end inside a key tile) and decoding over a sliced history."""
+    cfg = U.config(TENSOR_CORE_SHAPES[name], width=40)
+    W = U.weights(cfg, seed=21)
+    t = toks(330, seed=7)
+    want = U.oracle_logits(cfg, W, t)
+    assert U.rel_err(U.run_portions(cfg, W, t, [100, 3, 150, 64], page_size=16), want) < F32_TOL
+    e16 = U.row_errs(U.run_whole(cfg, W, t, "bfloat16", page_size=16), want)
+    assert float(np.quantile(e16, 0.8)) < 3e-2 and float(e16.max()) < 0.3
+    e16 = U.row_errs(U.run_portions(cfg, W, t, [100, 3, 150, 64], "bfloat16", page_size=16), want)
+    assert float(np.quantile(e16, 0.8)) < 3e-2 and float(e16.max()) < 0.3
+
+
+def test_gated_linear_attention_with_heads_above_128():
+    cfg = U.config([(U.parallel(left_scale=0.3, r_heads=1, r_dim=136, r_vdim=144, tau=8.0), None)], width=24)
+    W = U.weights(cfg, seed=13)
+    t = toks(100, seed=5)
+    assert U.rel_err(U.run_portions(cfg, W, t, [70, 2, 20]), U.oracle_logits(cfg, W, t)) < F32_TOL
+
+
 def test_attention_over_slices_of_the_history():
     """A single decoding sequence with a long history has its keys cut into slices that a second kernel merges; both weight
     forms, in prompts and decoding, against the oracle."""
@@ -182,10 +215,9 @@ def test_far_keys_and_page_borders_with_peaked_weights(decode_tail):
     assert U.rel_err(got, want) < 1e-4
 
 
-def _planted(kind):
-    """Hand-made weights for one layer of width 8 with one-hot token embeddings (layer norms keep a one-hot row's pattern):
+def _planted(kind, n=8):
+    """Hand-made weights for one layer of width n with one-hot token embeddings (layer norms keep a one-hot row's pattern):
     the query of token 2 points at the key of token 1 and at nothing else."""
-    n = 8
     if kind == "softmax":
         cfg = U.config([(U.parallel(heads=1, kv_heads=1, dim=n, vdim=n, rot_dims=0, scale=1.0, right_scale=0.0, r_heads=1, r_dim=4, r_vdim=4,
                                     rank=2), None)], vocab=n, width=n, embed_scale=1.0, logit_scale=1.0)
@@ -214,13 +246,12 @@ def _planted(kind):
     return cfg, W
 
 
-@pytest.mark.parametrize("kind", ["softmax", "sigmoid"])
-def test_a_key_planted_far_back_is_found(kind):
+@pytest.mark.parametrize("kind,n,dtype", [("softmax", 8, "float32"), ("sigmoid", 8, "float32"), ("softmax", 16, "bfloat16"), ("sigmoid", 16, "bfloat16")])
+def test_a_key_planted_far_back_is_found(kind, n, dtype):
     """Token 1 occurs once among 260 tokens; the last token (2) looks for it.  With sigmoid weights under a bias of -30 only
     that key gets a weight at all; with softmax it takes nearly all of it.  The output at the last position then changes with
     the planted key, wherever it stands: next to a page border on either side, at the very start, or just before the query."""
-    cfg, W = _planted(kind)
-    n = 8
+    cfg, W = _planted(kind, n)
     base = [int(x) for x in np.random.default_rng(1).integers(3, n, 260)]
     base[-1] = 2
     without = U.oracle_logits(cfg, W, base)[-1]
@@ -230,14 +261,14 @@ def test_a_key_planted_far_back_is_found(kind):
         want = U.oracle_logits(cfg, W, t)
         assert np.abs(want[-1] - without).max() > 0.05  # the planted key decides the output
         for tail in (0, 3):  # the query inside a prompt portion, and decoded alone
-            e = U.engine(cfg, W, pool_tokens=320, page_size=64)
+            e = U.engine(cfg, W, dtype, pool_tokens=320, page_size=64)
             f = U.Feeder(e)
             f.step([("a", t, 260 - tail)])
             for _ in range(tail):
                 f.step([("a", t, 1)])
             got = f.end("a")
             e.close()
-            assert U.rel_err(got, want) < 1e-4, (where, tail)
+            assert U.rel_err(got, want) < (1e-4 if dtype == "float32" else 2e-2), (where, tail)
 
 
 def test_sigmoid_bias_and_temperature_per_head():
