@@ -849,6 +849,9 @@ def run_motolix(args):
     batch, plen, vocab = args.batch or 8, args.prompt_len, 32000
     rng = np.random.default_rng(0)
     out = []
+    clocks = ClockSampler(0)
+    clocks.start()
+    clocks.mark_start()
     for key in want:
         W, ff = sizes[key]
         H = W // 128
@@ -916,8 +919,10 @@ def run_motolix(args):
             rec[f"llama_{depth}_layers"] = measure(eng)
             eng.close()
         out.append(rec)
+    clocks.mark_end()
     line = {"metric": "motolix_vs_llama_equal_size", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-            "dtype": "bf16", "data": "synthetic (random weights, uniform random tokens)", "higher_is_better": True, "sizes": out}
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random tokens)", "higher_is_better": True, "sizes": out,
+            "clocks": clocks.stop()}
     print(json.dumps(line))
     return 0
 

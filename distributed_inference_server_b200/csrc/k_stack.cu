@@ -324,7 +324,8 @@ cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long 
 }
 
 template <bool F32>
-__global__ void stack_final_ln_kernel(const float *x, const int *row_map, const float *w, const float *b, void *out, int W, float eps) {
+__global__ void stack_final_ln_kernel(const float *x, const int *row_map, const float *w, const float *b, void *out, int W, float eps,
+                                      float scale) {
   __shared__ float sh[32];
   const long long r = blockIdx.x;
   const float *xr = x + (long long)(row_map ? row_map[r] : r) * W;
@@ -334,12 +335,12 @@ __global__ void stack_final_ln_kernel(const float *x, const int *row_map, const 
   float q = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dvi = xr[i] - mean; q += dvi * dvi; }
   const float k = rsqrtf(block_sum(q, sh) / (float)W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, (xr[i] - mean) * k * w[i] + b[i]);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) st_el<F32>(out, r * W + i, ((xr[i] - mean) * k * w[i] + b[i]) * scale);
 }
 cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
-                                  float eps, cudaStream_t st) {
-  if (f32) stack_final_ln_kernel<true><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps);
-  else stack_final_ln_kernel<false><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps);
+                                  float eps, float scale, cudaStream_t st) {
+  if (f32) stack_final_ln_kernel<true><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps, scale);
+  else stack_final_ln_kernel<false><<<R, 256, 0, st>>>(x, row_map, w, b, out, W, eps, scale);
   return cudaGetLastError();
 }
 
@@ -485,13 +486,14 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 template <bool F32, int ACT>
-__global__ void stack_glu_kernel(const float *__restrict__ gu, const float *__restrict__ bias, void *__restrict__ act, const int *rows_ptr,
-                                 int M, int ff, float limit) {
+__global__ void stack_glu_kernel(const float *__restrict__ gu, int n_part, long long stride, const float *__restrict__ bias,
+                                 void *__restrict__ act, const int *rows_ptr, int M, int ff, float limit) {
   const int rows = rows_ptr ? min(M, rows_ptr[0]) : M;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const float *gr = gu + (long long)r * 2 * ff;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
       float g = gr[c] + (bias ? bias[c] : 0.f), u = gr[ff + c] + (bias ? bias[ff + c] : 0.f);
+      for (int k = 1; k < n_part; k++) { g += gr[(long long)k * stride + c]; u += gr[(long long)k * stride + ff + c]; }
       float v;
       if (ACT == DIS_ACT_GELU_TANH) v = gelu_tanh_(g) * u;
       else {
@@ -503,17 +505,17 @@ __global__ void stack_glu_kernel(const float *__restrict__ gu, const float *__re
     }
   }
 }
-cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
-                             int kind, cudaStream_t st) {
+cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, const float *bias, void *act, bool f32, const int *rows_ptr,
+                             int M, int ff, float limit, int kind, cudaStream_t st) {
   if (M <= 0) return cudaSuccess;
   // few rows: the columns are spread over grid.y as well
   const dim3 grid(std::min(M, 148 * 16), M >= 512 ? 1 : std::min((ff + 255) / 256, 16));
   if (kind == DIS_ACT_GELU_TANH) {
-    if (f32) stack_glu_kernel<true, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
-    else stack_glu_kernel<false, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+    if (f32) stack_glu_kernel<true, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
+    else stack_glu_kernel<false, DIS_ACT_GELU_TANH><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
   } else {
-    if (f32) stack_glu_kernel<true, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
-    else stack_glu_kernel<false, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, bias, act, rows_ptr, M, ff, limit);
+    if (f32) stack_glu_kernel<true, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
+    else stack_glu_kernel<false, DIS_ACT_CLAMPED><<<grid, 256, 0, st>>>(gu, n_part, stride, bias, act, rows_ptr, M, ff, limit);
   }
   return cudaGetLastError();
 }

@@ -1124,9 +1124,14 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
     RET_CUDA(sublayer_in(norm_w(L, 2), norm_b(L, 2), L.canon2, Rn.cstate2));
     if (lc.mlp == DIS_MLP_DENSE) {
       const int ff = lc.ff;
+      // the gated unit sums the slices of its input product itself and adds the bias the product left out
       const float *gu_bias = nullptr;
-      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias));
-      RET_CUDA(launch_stack_glu(M.proj, gu_bias, M.act, f32, nullptr, T, ff, lc.limit, lc.mlp_act, stream)); kl++;
+      RET_CUDA(gemm(M.hc, f32, W, L.w_gu, 0, reinterpret_cast<const float *>(L.b_gu.ptr), M.proj, T, 2 * ff, W, cap_tokens, &gu_bias, true));
+      const bool sliced = pend_parts > 1 || pend_bias;
+      RET_CUDA(launch_stack_glu(sliced ? pend_src : M.proj, sliced ? pend_parts : 1, pend_stride, sliced ? pend_bias : gu_bias, M.act, f32, nullptr,
+                                T, ff, lc.limit, lc.mlp_act, stream));
+      kl++;
+      pend_parts = 1; pend_bias = nullptr;
       RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, reinterpret_cast<const float *>(L.b_down.ptr), M.y, T, W, ff, cap_tokens, nullptr, later));
     } else {
       const int ff = lc.ff, E = lc.experts, top = lc.top, rows = T * top;
@@ -1150,7 +1155,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
           RET_CUDA(launch_gemm_partial(*wm, xm, M.proj + (size_t)off * 2 * ff, cnt, 2 * ff, W, 0, 1, stream));
           off += cnt; kl++;
         }
-        RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
+        RET_CUDA(launch_stack_glu(M.proj, 1, 0, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
         off = 0;
         for (int e = 0; e < E; e++) {
           const int cnt = M.h_counts[e];
@@ -1173,7 +1178,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       g.out = M.proj; g.ldo = 2 * ff; g.M = rows; g.N = 2 * ff; g.K = W;
       g.tiles = M.tiles; g.max_tiles = tiles_cap;
       RET_CUDA(launch_stack_gemm(g, stream));
-      RET_CUDA(launch_stack_glu(M.proj, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
+      RET_CUDA(launch_stack_glu(M.proj, 1, 0, nullptr, M.act, f32, nullptr, rows, ff, lc.limit, lc.mlp_act, stream));
       StackGemm dn;
       dn.A = M.act; dn.a_f32 = f32; dn.lda = ff;
       dn.W = L.w_down.ptr; dn.w_f32 = L.w_down.f32; dn.ldw = ff; dn.w_bs = (long long)W * ff;
@@ -1190,11 +1195,11 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
   else { RET_CUDA(launch_stack_resid_norm(M.x, pend_y, pend_post, nullptr, nullptr, T, W, eps, stream)); kl++; }
   if (R <= 0) return cudaSuccess;
   if (ln) RET_CUDA(launch_stack_final_ln(M.x, mt.d<int>(mt.o_rowmap), reinterpret_cast<const float *>(M.final_w.ptr),
-                                         reinterpret_cast<const float *>(M.final_b.ptr), M.xr, f32, R, W, eps, stream));
+                                         reinterpret_cast<const float *>(M.final_b.ptr), M.xr, f32, R, W, eps, M.c.logit_scale, stream));
   else RET_CUDA(launch_stack_final_norm(M.x, mt.d<int>(mt.o_rowmap), M.final_g, M.xr, f32, R, W, eps, stream));
   kl++;
   RET_CUDA(gemm(M.xr, f32, W, M.head, 0, nullptr, M.logits, R, M.c.vocab, W, M.max_rows));
-  if (M.c.logit_scale != 1.f) { RET_CUDA(launch_stack_scale(M.logits, (long long)R * M.c.vocab, M.c.logit_scale, stream)); kl++; }
+  if (!ln && M.c.logit_scale != 1.f) { RET_CUDA(launch_stack_scale(M.logits, (long long)R * M.c.vocab, M.c.logit_scale, stream)); kl++; }
   const float *temp = mt.d<float>(mt.o_temp), *topp = mt.d<float>(mt.o_topp);
   const unsigned long long *seed = mt.d<unsigned long long>(mt.o_seed), *step = mt.d<unsigned long long>(mt.o_step);
   float *d_logprob = reinterpret_cast<float *>(M.d_out + M.max_rows);

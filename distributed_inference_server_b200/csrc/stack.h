@@ -63,8 +63,9 @@ cudaError_t launch_stack_boundary_single(float *x, const float *y, int n_part, l
 cudaError_t launch_stack_boundary_ln(float *x, const float *y, int n_part, long long stride, const float *bias, const float *post_w,
                                      const float *post_b, const float *pre_w, const float *pre_b, float *hn, void *hc, const float *x0,
                                      void *cat, bool f32, int T, int W, float eps, cudaStream_t st);
+// out = LN(x[row_map[r]]) * scale: a factor on the logits is applied to the head's input (head (s v) = s (head v))
 cudaError_t launch_stack_final_ln(const float *x, const int *row_map, const float *w, const float *b, void *out, bool f32, int R, int W,
-                                  float eps, cudaStream_t st);
+                                  float eps, float scale, cudaStream_t st);
 cudaError_t launch_stack_scale(float *v, long long n, float s, cudaStream_t st);
 cudaError_t launch_stack_copy_act(const float *hn, void *hc, bool f32, long long n, cudaStream_t st);
 // proj [T][ld]: q at 0, k at H*d, v at 2*H*d (pre-activation).  state [slots][H][d][dv].  o [T][H*dv] fp32.
@@ -154,9 +155,10 @@ cudaError_t launch_stack_latent_softmax(const float *S, int rows, int ld, const 
                                         uint16_t *P, cudaStream_t st);
 // kind DIS_ACT_CLAMPED: act = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit);
 // DIS_ACT_GELU_TANH: act = gelu_tanh(g) u.  gu [M][2*ff] (gate | up)
-// bias (or null): [2*ff], added to gu here when the product that made gu left it out
-cudaError_t launch_stack_glu(const float *gu, const float *bias, void *act, bool f32, const int *rows_ptr, int M, int ff, float limit,
-                             int kind, cudaStream_t st);
+// gu may come as n_part split-K slices (slice stride `stride`), summed here; bias (or null): [2*ff], added here when the product
+// that made gu left it out
+cudaError_t launch_stack_glu(const float *gu, int n_part, long long stride, const float *bias, void *act, bool f32, const int *rows_ptr,
+                             int M, int ff, float limit, int kind, cudaStream_t st);
 // Router: logits in fp32 from hc and the fp32 router matrix; top-k by value (lowest index wins a tie); softmax over the chosen.
 cudaError_t launch_stack_route(const void *hc, bool f32, const float *router, int T, int W, int E, int top, int *idx, float *wt,
                                cudaStream_t st);
