@@ -14,7 +14,7 @@
 //   partial : out[s][t][n] fp32, s = split-K slice (consumers sum the slices: add_rmsnorm,
 //             rope_kv_write, the sampler reads slice 0 of the lm_head logits)
 //   silu    : two accumulators (gate rows, up rows of the fused [2I][K] weight) ->
-//             act[t][n] = bf16(silu(gate) * up)
+//             act[t][n] = bf16(silu(gate) * up), or gelu_tanh(gate) * up (launch_gemm_glu, act_kind 1)
 //
 // Roofline: HBM-bound for T <= ~128 (AI ~ T flop/B against ~210 flop/B machine balance).
 // Algorithmic bytes per launch = 2*N*K (weights) + 2*T*K (activations) + 4*S*T*N (partials) or 2*T*I.
@@ -54,7 +54,7 @@ template <int BN, bool kDual>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                     float *__restrict__ out_partial, uint16_t *__restrict__ out_act, int T, int N, int K,
-                    int w_row0, int up_row_off, int kb_per_split, int tile_rows, int n_stages, int early_tma) {
+                    int w_row0, int up_row_off, int kb_per_split, int tile_rows, int n_stages, int early_tma, int act_kind) {
   using Cfg = GemmCfg<BN, kDual>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -170,7 +170,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             const int t = t0 + c + jj;
             if (t < T) {
               const float gv = __uint_as_float(g[jj]), uv = __uint_as_float(u[jj]);
-              out_act[(size_t)t * N + n] = float_to_bf16_bits((gv / (1.0f + expf(-gv))) * uv);
+              // act_kind 0: silu(gate) * up; 1: gelu_tanh(gate) * up
+              const float av = act_kind == 1 ? 0.5f * gv * (1.f + tanhf(0.7978845608028654f * (gv + 0.044715f * gv * gv * gv)))
+                                             : gv / (1.0f + expf(-gv));
+              out_act[(size_t)t * N + n] = float_to_bf16_bits(av * uv);
             }
           }
         }
@@ -250,7 +253,7 @@ int gemm_pick_split_k(int T, int N, int K) {
 
 template <int BN, bool kDual>
 static cudaError_t gemm_launch(const TmaMap &w_map, const TmaMap &x_map, float *out, uint16_t *act, int T, int N,
-                               int K, int w_row0, int up_off, int split_k, int tile_rows, cudaStream_t st) {
+                               int K, int w_row0, int up_off, int split_k, int tile_rows, cudaStream_t st, int act_kind = 0) {
   using Cfg = GemmCfg<BN, kDual>;
   auto kern = gemm_tcgen05_kernel<BN, kDual>;
   static DeviceOnce once;
@@ -280,7 +283,7 @@ static cudaError_t gemm_launch(const TmaMap &w_map, const TmaMap &x_map, float *
   static int early = -1;
   if (early < 0) { const char *e = getenv("DIS_GEMM_EARLY_TMA"); early = (e && atoi(e) == 0) ? 0 : 1; }
   return launch_k(kern, grid, dim3(kGemmThreads), (size_t)smem, st, *reinterpret_cast<const CUtensorMap *>(&w_map),
-                  *reinterpret_cast<const CUtensorMap *>(&x_map), out, act, T, N, K, w_row0, up_off, per, tile_rows, stages, early);
+                  *reinterpret_cast<const CUtensorMap *>(&x_map), out, act, T, N, K, w_row0, up_off, per, tile_rows, stages, early, act_kind);
 }
 
 cudaError_t launch_gemm_partial(const TmaMap &w_map, const TmaMap &x_map, float *out, int T, int N, int K,
@@ -303,15 +306,19 @@ int gemm_pick_tile_rows(int N) {
   return r > kBM ? kBM : (r < 8 ? 8 : r);
 }
 
-cudaError_t launch_gemm_silu(const TmaMap &w_map, const TmaMap &x_map, uint16_t *act, int T, int I, int K,
-                             int w_row0, int tile_rows, cudaStream_t st) {
+cudaError_t launch_gemm_glu(const TmaMap &w_map, const TmaMap &x_map, uint16_t *act, int T, int I, int K,
+                            int w_row0, int tile_rows, int act_kind, cudaStream_t st) {
   if (T <= 0) return cudaSuccess;
   switch (gemm_token_tile(T)) {
-    case 32: return gemm_launch<32, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st);
-    case 64: return gemm_launch<64, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st);
-    case 128: return gemm_launch<128, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st);
-    default: return gemm_launch<256, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st);
+    case 32: return gemm_launch<32, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st, act_kind);
+    case 64: return gemm_launch<64, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st, act_kind);
+    case 128: return gemm_launch<128, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st, act_kind);
+    default: return gemm_launch<256, true>(w_map, x_map, nullptr, act, T, I, K, w_row0, I, 1, tile_rows, st, act_kind);
   }
+}
+cudaError_t launch_gemm_silu(const TmaMap &w_map, const TmaMap &x_map, uint16_t *act, int T, int I, int K,
+                             int w_row0, int tile_rows, cudaStream_t st) {
+  return launch_gemm_glu(w_map, x_map, act, T, I, K, w_row0, tile_rows, 0, st);
 }
 
 }  // namespace dis
