@@ -293,8 +293,37 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t &r0, uint3
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {  // src_bytes 0: zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  return (uint32_t)float_to_bf16_bits(lo) | ((uint32_t)float_to_bf16_bits(hi) << 16);
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {  // round to nearest even, one instruction
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float ex2_(float x) {  // 2^x, flushing results below the normal range to zero; 2^(-inf) = 0
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Scores of one 64-key tile -> sigmoid weights, or scaled scores and the rows' running maxima (softmax).  MASKED: the tile
+// reaches past a row's position or the slice's end, so every element is checked; interior tiles skip the checks.
+template <bool SIG, bool MASKED>
+__device__ __forceinline__ void attn_tile_weights(float (&sacc)[kMmKeys / 8][4], float (&mnew)[2], int k0, int qd, const int (&r_pos)[2],
+                                                  int k_end, const float (&tmp_h)[2], const float (&pb_h)[2], float scale2) {
+#pragma unroll
+  for (int j = 0; j < kMmKeys / 8; j++)
+#pragma unroll
+    for (int q4 = 0; q4 < 4; q4++) {
+      const int e = q4 >> 1;
+      bool vis = true;
+      if (MASKED) { const int kp = k0 + j * 8 + qd * 2 + (q4 & 1); vis = kp <= r_pos[e] && kp < k_end; }
+      float sv = sacc[j][q4];
+      if (SIG) {
+        float rc;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.f + ex2_(-fmaf(sv, tmp_h[e], pb_h[e]))));
+        sv = vis ? rc : 0.f;
+      } else { sv = vis ? sv * scale2 : -INFINITY; mnew[e] = fmaxf(mnew[e], sv); }
+      sacc[j][q4] = sv;
+    }
 }
 
 bool stack_attn_mma_ok(const StackAttn &c, bool f32) {
@@ -423,28 +452,15 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
       // exponential is one ex2.  Only a tile that reaches past a row's position or the slice's end needs the mask.
       const bool masked = k0 + kMmKeys - 1 > pos_first + (warp * 16) / R || k0 + kMmKeys > k_end;
       float mnew[2] = {mrow[0], mrow[1]};
-#pragma unroll
-      for (int j = 0; j < kMmKeys / 8; j++)
-#pragma unroll
-        for (int q4 = 0; q4 < 4; q4++) {
-          const int e = q4 >> 1;
-          bool vis = true;
-          if (masked) { const int kp = k0 + j * 8 + qd * 2 + (q4 & 1); vis = kp <= r_pos[e] && kp < k_end; }
-          float sv = sacc[j][q4];
-          if (SIG) {
-            float rc;
-            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.f + exp2f(-fmaf(sv, tmp_h[e], pb_h[e]))));
-            sv = vis ? rc : 0.f;
-          } else { sv = vis ? sv * scale2 : -INFINITY; mnew[e] = fmaxf(mnew[e], sv); }
-          sacc[j][q4] = sv;
-        }
+      if (masked) attn_tile_weights<SIG, true>(sacc, mnew, k0, qd, r_pos, k_end, tmp_h, pb_h, scale2);
+      else attn_tile_weights<SIG, false>(sacc, mnew, k0, qd, r_pos, k_end, tmp_h, pb_h, scale2);
       if (!SIG) {
         float corr[2];
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           mnew[e] = fmaxf(mnew[e], __shfl_xor_sync(0xffffffffu, mnew[e], 1));
           mnew[e] = fmaxf(mnew[e], __shfl_xor_sync(0xffffffffu, mnew[e], 2));
-          corr[e] = mrow[e] == -INFINITY ? 0.f : exp2f(mrow[e] - mnew[e]);
+          corr[e] = mrow[e] == -INFINITY ? 0.f : ex2_(mrow[e] - mnew[e]);
           mrow[e] = mnew[e];
           lrow[e] *= corr[e];
         }
@@ -454,7 +470,7 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) {
             const int e = q4 >> 1;
-            const float pv = exp2f(sacc[j][q4] - msub[e]);  // 2^(-inf) = 0 for the masked
+            const float pv = ex2_(sacc[j][q4] - msub[e]);  // 2^(-inf) = 0 for the masked
             sacc[j][q4] = pv;
             lrow[e] += pv;
           }
