@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
                                                                      float *state, StackSpans sp, float *__restrict__ o, int H, int d,
                                                                      int dv, float *seg, float *seg_a, int max_seg) {
   extern __shared__ __align__(16) float shm[];
-  constexpr int DP = RI * 8, DVP = RJ * 32, LD = kLightTok * ((GATE ? 3 : 2) * DP + DVP) / 256;
+  constexpr int DP = RI * 8, DVP = RJ * 32;
   // heads vary fastest over the grid: the CTAs that run at the same time then read whole rows of the projections rather than
   // one head's columns at a stride of a row, which would keep most memory channels idle
   const int h = blockIdx.x % H, sc = blockIdx.x / H;
@@ -125,19 +125,31 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
       }
       S[ii][jj] = v;
     }
+  // Staging: a token's inputs are `per` numbers (q, k, v of this head, and with GATE its d decays); per <= 512, so every thread
+  // owns at most two of these columns for all tokens.  Where a column comes from and where it goes is worked out once.
   const int per = (GATE ? 3 : 2) * d + dv;
-  float tmp[LD];
+  const float *src[2];
+  long long sstride[2];
+  float *sdst[2];
+  int dstride[2];
+  float mul[2];
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    const int c = threadIdx.x + u * 256;
+    src[u] = nullptr; sstride[u] = ld; sdst[u] = qs; dstride[u] = DP; mul[u] = 1.f;
+    if (c < d) { src[u] = proj + col.q + (long long)h * d + c; sdst[u] = qs + c; mul[u] = GATE ? qscale : 1.f; }
+    else if (c < 2 * d) { src[u] = proj + col.k + (long long)h * d + (c - d); sdst[u] = ks + (c - d); }
+    else if (c < 2 * d + dv) { src[u] = proj + col.v + (long long)h * dv + (c - 2 * d); sdst[u] = vs + (c - 2 * d); dstride[u] = DVP; }
+    else if (c < per) { src[u] = dec + (long long)h * d + (c - 2 * d - dv); sstride[u] = (long long)H * d; sdst[u] = as + (c - 2 * d - dv); }
+  }
+  float tmp[2 * kLightTok];
   auto fetch = [&](int t0) {
     const int ct = min(kLightTok, n - t0);
 #pragma unroll
-    for (int u = 0; u < LD; u++) {
-      const int e = threadIdx.x + u * 256, t = e / per, c = e - t * per;
+    for (int t = 0; t < kLightTok; t++) {
       if (t < ct) {
-        const float *row = proj + (long long)(first + t0 + t) * ld;
-        if (c < d) tmp[u] = row[col.q + (long long)h * d + c];
-        else if (c < 2 * d) tmp[u] = row[col.k + (long long)h * d + (c - d)];
-        else if (c < 2 * d + dv) tmp[u] = row[col.v + (long long)h * dv + (c - 2 * d)];
-        else tmp[u] = dec[(long long)(first + t0 + t) * H * d + (long long)h * d + (c - 2 * d - dv)];
+        if (src[0]) tmp[2 * t] = src[0][(long long)(first + t0 + t) * sstride[0]];
+        if (src[1]) tmp[2 * t + 1] = src[1][(long long)(first + t0 + t) * sstride[1]];
       }
     }
   };
@@ -146,13 +158,10 @@ __global__ void __launch_bounds__(256, 2) stack_lightning_reg_kernel(const float
     const int ct = min(kLightTok, n - t0);
     __syncthreads();
 #pragma unroll
-    for (int u = 0; u < LD; u++) {
-      const int e = threadIdx.x + u * 256, t = e / per, c = e - t * per;
+    for (int t = 0; t < kLightTok; t++) {
       if (t < ct) {
-        if (c < d) qs[t * DP + c] = GATE ? tmp[u] * qscale : silu_(tmp[u]);
-        else if (c < 2 * d) ks[t * DP + (c - d)] = GATE ? tmp[u] : silu_(tmp[u]);
-        else if (c < 2 * d + dv) vs[t * DVP + (c - 2 * d)] = GATE ? tmp[u] : silu_(tmp[u]);
-        else as[t * DP + (c - 2 * d - dv)] = tmp[u];
+        if (src[0]) sdst[0][t * dstride[0]] = GATE ? tmp[2 * t] * mul[0] : silu_(tmp[2 * t]);
+        if (src[1]) sdst[1][t * dstride[1]] = GATE ? tmp[2 * t + 1] * mul[1] : silu_(tmp[2 * t + 1]);
       }
     }
     if (t0 + kLightTok < n) fetch(t0 + kLightTok);
