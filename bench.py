@@ -857,10 +857,10 @@ def run_motolix(args):
         H = W // 128
         G = max(1, H // 4)
         att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                                              "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+                                              "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
         par = {"type": "parallel", "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                                                       "rot": {"base": 10000.0, "dims": 128}},
-                                             "right": {"heads": H, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16},
+                                             "right": {"heads": H, "dim": 64, "vdim": 128, "tau": 8.0, "rank": 32},
                                              "left_scale": 0.7, "right_scale": 0.7}}
         dense = {"kind": "dense", "ff": ff}
         variants = {"mixed_loop": ([par, att, par, att], (1, 3, 2))}

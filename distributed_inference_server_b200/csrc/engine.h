@@ -181,6 +181,7 @@ struct Engine {
   bool stack_lat_mma = false; // some latent layer runs the mma.sync attention kernel (64-key tiles)
   int stack_max_ctx = 0;      // longest history (tokens in the cache after the pass) among the sequences of the pass being built
   size_t stack_lat_rec = 0;   // floats of one token's slice record in split latent attention: max over layers of heads * (kv_rank + 2)
+  bool stack_persist = true;  // prompt-sized bf16 products on the persistent tcgen05 kernels (DIS_STACK_PERSIST=0: A/B runs)
   bool stack_tc = true;  // bf16 dense projections on the tcgen05 GEMM (DIS_STACK_TC=0: the fp32-FMA product everywhere, A/B runs)
   std::map<std::tuple<const void *, uint64_t, uint64_t, uint32_t>, TmaMap> stack_maps;  // (base, rows, cols, box rows)
   const TmaMap *stack_map(const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);

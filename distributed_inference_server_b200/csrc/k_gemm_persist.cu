@@ -194,7 +194,7 @@ __device__ __forceinline__ void named_bar_arrive(int id, int n) { asm volatile("
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_persist_pair_kernel(const __grid_constant__ CUtensorMap w_map64, const __grid_constant__ CUtensorMap x_map,
                          uint16_t *__restrict__ out_act, int T, int I, int K, int w_row0, int tiles_n, int tiles_t,
-                         int t_fast) {
+                         int t_fast, int act_kind) {
   constexpr int BN = 256, kHalf = 64;
   using Cfg = PersistCfg<256, false>;
   extern __shared__ uint8_t smem_raw[];
@@ -311,7 +311,10 @@ gemm_persist_pair_kernel(const __grid_constant__ CUtensorMap w_map64, const __gr
             if (t < T) {
               const float other = take[jj * 32 + lane], mine = __uint_as_float(kv[jj]);
               const float gv = is_up ? other : mine, uv = is_up ? mine : other;
-              out_act[(size_t)t * I + n] = float_to_bf16_bits((gv / (1.0f + expf(-gv))) * uv);
+              // act_kind 0: silu(gate) * up; 1: gelu_tanh(gate) * up
+              const float av = act_kind == 1 ? 0.5f * gv * (1.f + tanhf(0.7978845608028654f * (gv + 0.044715f * gv * gv * gv)))
+                                             : gv / (1.0f + expf(-gv));
+              out_act[(size_t)t * I + n] = float_to_bf16_bits(av * uv);
             }
           }
         }
@@ -368,6 +371,11 @@ cudaError_t launch_gemm_persist_partial(const TmaMap &w_map, const TmaMap &x_map
 // act[t][n] = bf16(silu(gate) * up).
 cudaError_t launch_gemm_persist_silu(const TmaMap &w_map64, const TmaMap &x_map256, uint16_t *act, int T, int I, int K,
                                      int w_row0, cudaStream_t st) {
+  return launch_gemm_persist_glu(w_map64, x_map256, act, T, I, K, w_row0, 0, st);
+}
+// the same with the gate's activation chosen: act_kind 0 = silu, 1 = gelu_tanh
+cudaError_t launch_gemm_persist_glu(const TmaMap &w_map64, const TmaMap &x_map256, uint16_t *act, int T, int I, int K,
+                                    int w_row0, int act_kind, cudaStream_t st) {
   if (T <= 0) return cudaSuccess;
   using Cfg = PersistCfg<256, false>;
   constexpr int smem = Cfg::kSmemBytes + kPairXchgBytes;
@@ -385,7 +393,7 @@ cudaError_t launch_gemm_persist_silu(const TmaMap &w_map64, const TmaMap &x_map2
   const int t_fast = 2LL * I > (long long)T ? 1 : 0;
   return launch_k(gemm_persist_pair_kernel, dim3(grid), dim3(kGemmThreads), (size_t)smem, st,
                   *reinterpret_cast<const CUtensorMap *>(&w_map64), *reinterpret_cast<const CUtensorMap *>(&x_map256), act, T, I,
-                  K, w_row0, tiles_n, tiles_t, t_fast);
+                  K, w_row0, tiles_n, tiles_t, t_fast, act_kind);
 }
 
 }  // namespace dis

@@ -117,6 +117,8 @@ cudaError_t launch_gemm_persist_partial(const TmaMap &w_map128, const TmaMap &x_
                                         int w_row0, cudaStream_t st);
 cudaError_t launch_gemm_persist_silu(const TmaMap &w_map64, const TmaMap &x_map256, uint16_t *act, int T, int I, int K,
                                      int w_row0, cudaStream_t st);
+cudaError_t launch_gemm_persist_glu(const TmaMap &w_map64, const TmaMap &x_map256, uint16_t *act, int T, int I, int K,
+                                    int w_row0, int act_kind, cudaStream_t st);
 cudaError_t launch_gemm_silu(const TmaMap &w_map, const TmaMap &x_map, uint16_t *act, int T, int I, int K,
                              int w_row0, int tile_rows, cudaStream_t st);
 // the same with the gate's activation chosen: act_kind 0 = silu, 1 = gelu_tanh

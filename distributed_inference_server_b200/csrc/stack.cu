@@ -535,6 +535,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.lat_part), M.lat_part_elems * 4));
   }
   if (const char *g = getenv("DIS_STACK_TC")) stack_tc = atoi(g) != 0;
+  if (const char *g = getenv("DIS_STACK_PERSIST")) stack_persist = atoi(g) != 0;
   if (!M.f32 && stack_tc) {
     M.scratch_elems = 2 * cap * std::max(max_proj, (size_t)W);
     ENG_CUDA(alloc(reinterpret_cast<void **>(&M.scratch), M.scratch_elems * 4));
@@ -907,7 +908,16 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       if ((size_t)s * Mrows * N > M.scratch_elems) s = 1;
       kl++;
       if (s == 1 && bias && later_bias) { *later_bias = bias; bias = nullptr; }
-      if (s == 1 && !bias) return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, stream);
+      if (s == 1 && !bias) {
+        // prompt-sized products with at least two tiles per SM: the persistent kernel (one CTA per SM walks the tiles, the
+        // accumulator double-buffered in TMEM), as the Llama path does
+        if (stack_persist && gemm_use_persist(Mrows, N, false)) {
+          const TmaMap *xm256 = stack_map(A, (uint64_t)a_rows, (uint64_t)K, 256);
+          if (!xm256) return cudaErrorInvalidValue;
+          return launch_gemm_persist_partial(*wm, *xm256, out, Mrows, N, K, 0, stream);
+        }
+        return launch_gemm_partial(*wm, *xm, out, Mrows, N, K, 0, 1, stream);
+      }
       if ((size_t)s * Mrows * N > M.scratch_elems) return cudaErrorInvalidValue;
       RET_CUDA(launch_gemm_partial(*wm, *xm, M.scratch, Mrows, N, K, 0, s, stream));
       if (later_sum) {  // the boundary kernel of a single-token pass sums the slices and adds the bias
@@ -1129,11 +1139,18 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       // split-K product below, whose slices the gated unit sums: at these widths a single pass over K leaves each CTA a
       // long thin loop (measured: 0.337 against 0.320 ms per step of four layers at width 1024).
       if (stack_tc && !f32 && lc.mlp_act == DIS_ACT_GELU_TANH && !L.b_gu.ptr && W % 8 == 0 && !L.w_gu.f32 && gemm_token_tile(T) >= 128) {
-        const int tr = 128;
-        const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, (uint32_t)gemm_token_tile(T));
-        const TmaMap *wm = stack_map(L.w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, (uint32_t)tr);
-        if (!xm || !wm) return cudaErrorInvalidValue;
-        RET_CUDA(launch_gemm_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tr, 1, stream));
+        if (stack_persist && gemm_use_persist(T, ff, true)) {  // paired gate / up tiles on the persistent kernel
+          const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, 256);
+          const TmaMap *wm = stack_map(L.w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, 64);
+          if (!xm || !wm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_persist_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, 1, stream));
+        } else {
+          const int tr = 128;
+          const TmaMap *xm = stack_map(M.hc, (uint64_t)cap_tokens, (uint64_t)W, (uint32_t)gemm_token_tile(T));
+          const TmaMap *wm = stack_map(L.w_gu.ptr, (uint64_t)2 * ff, (uint64_t)W, (uint32_t)tr);
+          if (!xm || !wm) return cudaErrorInvalidValue;
+          RET_CUDA(launch_gemm_glu(*wm, *xm, reinterpret_cast<uint16_t *>(M.act), T, ff, W, 0, tr, 1, stream));
+        }
         kl++;
         RET_CUDA(gemm(M.act, f32, ff, L.w_down, 0, nullptr, M.y, T, W, ff, cap_tokens, nullptr, later));
         pend_y = M.y; pend_post = norm_w(L, 3); pend_post_b = norm_b(L, 3);

@@ -133,6 +133,30 @@ def test_gated_linear_attention_with_heads_above_128():
     assert U.rel_err(U.run_portions(cfg, W, t, [70, 2, 20]), U.oracle_logits(cfg, W, t)) < F32_TOL
 
 
+def test_persistent_products_agree_with_the_tiled_ones(monkeypatch):
+    """A pass of 5120 prompt tokens is large enough for the persistent tensor-core products (plain: the input projection of a
+    wide parallel layer; paired gate / up tiles with the gelu epilogue).  The same pass with DIS_STACK_PERSIST=0 takes the
+    tiled products; both round the same operands to bfloat16, so the logits agree to accumulation order."""
+    cfg = U.config([(U.parallel(heads=8, kv_heads=2, dim=64, vdim=64, rot_dims=32, r_heads=8, r_dim=64, r_vdim=64, rank=16), U.dense(ff=1024))],
+                   width=128, vocab=64)
+    W = U.weights(cfg, seed=27)
+    seqs = [toks(640, vocab=64, seed=80 + i) for i in range(8)]
+    res = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("DIS_STACK_PERSIST", flag)
+        e = U.engine(cfg, W, "bfloat16", max_batch=8, pool_tokens=8 * 704, page_size=64, max_step_tokens=8 * 640, rows=64)
+        P = InferenceParams(max_tokens=1 << 20, temperature=0.0)
+        slots = [e.seq_add(sq, P) for sq in seqs]
+        for sl in slots:
+            e.seq_probe(sl, [5, 300, 638])
+        e.step(slots)
+        res.append(e.last_logits(e.last_logit_rows()).copy())
+        e.close()
+    assert res[0].shape == (8 * 4, 64)
+    assert U.rel_err(res[0], res[1]) < 1e-3
+    assert np.abs(res[0]).max() > 1e-2
+
+
 def test_attention_over_slices_of_the_history():
     """A single decoding sequence with a long history has its keys cut into slices that a second kernel merges; both weight
     forms, in prompts and decoding, against the oracle."""
