@@ -314,27 +314,46 @@ cudaError_t launch_stack_lightning(const float *proj, long long ld, const float 
 
 // ------------------------------------------------------------------------------------------------ gated linear attention
 // Decays: z[c] = b[c] + sum_r A2[c][r] u[r] with u the rank-sized bottleneck (columns a_off .. of proj, fp32), then
-// a[c] = sigmoid(z[c])^(1/tau) = exp(-softplus(-z[c]) / tau), everything fp32.  One block per token.
+// a[c] = sigmoid(z[c])^(1/tau) = exp(-softplus(-z[c]) / tau), everything fp32.  A block takes 16 tokens and 128 channels: the
+// tokens' u sit in shared memory, a thread reads its channel's row of A2 once and uses it for all 16 tokens.
+constexpr int kDecTok = 16;
 template <bool WF32>
 __global__ void __launch_bounds__(128) stack_gla_decay_kernel(const float *proj, long long ld, int a_off, const void *a2, const float *b,
-                                                              int n, int rank, float inv_tau, float *dec) {
-  extern __shared__ float u[];  // [rank]
-  const long long t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) u[r] = proj[t * ld + a_off + r];
+                                                              int T, int n, int rank, float inv_tau, float *dec) {
+  extern __shared__ float u[];  // [kDecTok][rank]
+  const int t0 = blockIdx.x * kDecTok, nt = min(kDecTok, T - t0);
+  for (int i = threadIdx.x; i < kDecTok * rank; i += blockDim.x) {
+    const int tt = i / rank, r = i - tt * rank;
+    u[i] = tt < nt ? proj[(long long)(t0 + tt) * ld + a_off + r] : 0.f;
+  }
   __syncthreads();
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    float z = b[c];
-    for (int r = 0; r < rank; r++) z = fmaf(ld_el<WF32>(a2, (long long)c * rank + r), u[r], z);
-    // -log sigmoid(z) = softplus(-z) = max(-z, 0) + log1p(exp(-|z|))
-    const float sp = fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)));
-    dec[t * n + c] = expf(-sp * inv_tau);
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  float z[kDecTok];
+#pragma unroll
+  for (int tt = 0; tt < kDecTok; tt++) z[tt] = b[c];
+  for (int r = 0; r < rank; r++) {
+    const float w = ld_el<WF32>(a2, (long long)c * rank + r);
+#pragma unroll
+    for (int tt = 0; tt < kDecTok; tt++) z[tt] = fmaf(w, u[tt * rank + r], z[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < kDecTok; tt++) {
+    if (tt < nt) {
+      // -log sigmoid(z) = softplus(-z) = max(-z, 0) + log1p(exp(-|z|))
+      const float sp = fmaxf(-z[tt], 0.f) + log1pf(expf(-fabsf(z[tt])));
+      dec[(long long)(t0 + tt) * n + c] = expf(-sp * inv_tau);
+    }
   }
 }
 cudaError_t launch_stack_gla_decay(const float *proj, long long ld, int a_off, const void *a2, bool w_f32, const float *b, int T, int n,
                                    int rank, float tau, float *dec, cudaStream_t st) {
   if (T <= 0) return cudaSuccess;
-  if (w_f32) stack_gla_decay_kernel<true><<<T, 128, (size_t)rank * 4, st>>>(proj, ld, a_off, a2, b, n, rank, 1.f / tau, dec);
-  else stack_gla_decay_kernel<false><<<T, 128, (size_t)rank * 4, st>>>(proj, ld, a_off, a2, b, n, rank, 1.f / tau, dec);
+  const dim3 grid((T + kDecTok - 1) / kDecTok, (n + 127) / 128);
+  const size_t sh = (size_t)kDecTok * rank * sizeof(float);
+  if (sh > 48 * 1024) return cudaErrorInvalidValue;
+  if (w_f32) stack_gla_decay_kernel<true><<<grid, 128, sh, st>>>(proj, ld, a_off, a2, b, T, n, rank, 1.f / tau, dec);
+  else stack_gla_decay_kernel<false><<<grid, 128, sh, st>>>(proj, ld, a_off, a2, b, T, n, rank, 1.f / tau, dec);
   return cudaGetLastError();
 }
 

@@ -159,7 +159,7 @@ int Engine::init_stack(const dis_engine_config *c, const dis_stack_config *sc) {
       L.n_act = H * dv;
       if (lc.mixer == DIS_MIX_PARALLEL) {
         const int Hr = lc.gla_heads, dr = lc.gla_dim, dvr = lc.gla_vdim;
-        if (Hr <= 0 || dr <= 0 || dvr <= 0 || lc.gla_rank <= 0 || !(lc.gla_tau > 0.f)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "gated linear attention needs heads, dim, vdim, rank and tau > 0");
+        if (Hr <= 0 || dr <= 0 || dvr <= 0 || lc.gla_rank <= 0 || lc.gla_rank > 768 || !(lc.gla_tau > 0.f)) return fail(DIS_ERR_INVALID_ARGUMENT, at + "gated linear attention needs heads, dim, vdim, a rank up to 768 and tau > 0");
         if ((dr > 128 || dvr > 128) && ((size_t)dr * dvr + 3 * dr + 9 * dvr) * 4 > 220 * 1024)
           return fail(DIS_ERR_INVALID_ARGUMENT, at + "gated linear attention: dim * vdim does not fit shared memory");
         L.gq_off = L.n_in; L.gk_off = L.gq_off + Hr * dr; L.gv_off = L.gk_off + Hr * dr; L.gg_off = L.gv_off + Hr * dvr;

@@ -133,6 +133,18 @@ def test_gated_linear_attention_with_heads_above_128():
     assert U.rel_err(U.run_portions(cfg, W, t, [70, 2, 20]), U.oracle_logits(cfg, W, t)) < F32_TOL
 
 
+@pytest.mark.parametrize("width", [40, 300, 600, 1100])
+def test_prompt_sized_passes_at_several_widths(width):
+    """A prompt of 1100 tokens in one pass at four widths (rows shorter and longer than a block of the boundary kernel), through a
+    looped layer (the [x ; x0] output).  Against the oracle in float32, and in bfloat16."""
+    cfg = U.config([(U.parallel(heads=1, kv_heads=1, r_heads=1), U.dense(ff=16))], width=width, loop=(0, 1, 2))
+    W = U.weights(cfg, seed=33)
+    t = toks(1100, seed=14)
+    want = U.oracle_logits(cfg, W, t)
+    assert U.rel_err(U.run_whole(cfg, W, t, pool_tokens=1152, page_size=64), want) < F32_TOL
+    assert U.bf16_close(U.run_whole(cfg, W, t, "bfloat16", pool_tokens=1152, page_size=64), want)
+
+
 def test_persistent_products_agree_with_the_tiled_ones(monkeypatch):
     """A pass of 5120 prompt tokens is large enough for the persistent tensor-core products (plain: the input projection of a
     wide parallel layer; paired gate / up tiles with the gelu epilogue).  The same pass with DIS_STACK_PERSIST=0 takes the
