@@ -17,14 +17,27 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", None)])
 def test_trace_replay_matches_the_plain_implementation(tmp_path, dtype, tol):
     cfg = U.config([(U.latent(), U.dense()), (U.lightning(), U.moe()), (U.latent(kv_from=0), None), (U.mingru(), U.dense())], vocab=90, width=40)
-    W = U.weights(cfg, seed=3)
+    _replay(tmp_path, dtype, tol, cfg, U.weights(cfg, seed=3), U.oracle_logits)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", None)])
+def test_trace_replay_of_a_motolix_model(tmp_path, dtype, tol):
+    """The same schedule through a looped Motolix model: attention pages and recurrent slots of every loop pass are handed on
+    from request to request."""
+    from tests import _motolix_util as M
+    cfg = M.config([(M.parallel(dim=16, vdim=16, rot_dims=8), M.dense()), (M.attention(dim=16, rot_dims=8, scaling=(4.0, 1.0, 4.0, 64)), M.dense()),
+                    (M.parallel(heads=2, kv_heads=1, r_heads=2), None)], vocab=90, width=40, loop=(0, 2, 2))
+    _replay(tmp_path, dtype, tol, cfg, M.weights(cfg, seed=3), M.oracle_logits)
+
+
+def _replay(tmp_path, dtype, tol, cfg, W, oracle_logits):
     model = tmp_path / "model"
     model.mkdir()
     (model / "config.json").write_text(json.dumps(cfg))
     write_safetensors(model / "model.safetensors", W)
     rng = np.random.default_rng(4)
     reqs = {k: rng.integers(0, 90, n).tolist() for k, n in [("a", 150), ("b", 70), ("c", 1), ("d", 64), ("e", 129), ("f", 40)]}
-    want = {k: U.oracle_logits(cfg, W, v) for k, v in reqs.items()}
+    want = {k: oracle_logits(cfg, W, v) for k, v in reqs.items()}
     # steps: (id, count) lists; at most four requests live, 320 tokens of pages (64 each) for 454 tokens in total
     plan = [[("a", 100), ("b", 2)], [("a", 1), ("b", 60), ("c", 1)], [("a", 1), ("b", 1), ("d", 64)], [("a", 48), ("b", 7), ("d", 0)],
             [("e", 3), ("f", 39)], [("e", 2), ("f", 1)], [("e", 124)]]
