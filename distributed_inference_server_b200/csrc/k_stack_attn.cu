@@ -429,7 +429,6 @@ __global__ void __launch_bounds__(kMmWarps * 32, 3) stack_attn_mma_kernel(const 
     }
     __syncthreads();
     if (warp_live && k0 <= warp_last_pos) {
-      const uint16_t *Kt = Ks + stage * kMmKeys * PITCH;
       // S = Q K^T: k-steps outside, key tiles inside, so that consecutive products go to different accumulators; one ldmatrix
       // brings the fragments of two key tiles (lane l: matrix l / 8 = (tile, column half), row l % 8)
       const uint32_t kt = ks_base + (uint32_t)(stage * kMmKeys * PITCH * 2);

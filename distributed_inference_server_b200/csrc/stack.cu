@@ -1028,7 +1028,7 @@ cudaError_t Engine::stack_forward(int T, int n_spans, int n_qb, int R, bool all_
       RET_CUDA(launch_stack_attn_prep(M.proj, N, L.q_off, L.k_off, L.v_off, in_bias, qkn, qkn ? qkn + (size_t)H * d : nullptr, L.freq, L.vfreq, sa,
                                       sp, M.qf, Rn.kpool, Rn.vpool, M.vrot, f32, d_page_table, max_pages, page_size, stream));
       RET_CUDA(launch_stack_attn(M.qf, Rn.kpool, Rn.vpool, f32, tpb, tpb ? tpb + H : nullptr, sa, sp, mt.d<int>(mt.o_kb_tok0),
-                                 mt.d<int>(mt.o_kb_len), stack_kb, stack_abq, d_page_table, max_pages, page_size, M.act, L.n_act, 0,
+                                 mt.d<int>(mt.o_kb_len), stack_kb, single ? 1 : stack_abq, d_page_table, max_pages, page_size, M.act, L.n_act, 0,
                                  par ? lc.mix_scale : 1.f, M.vrot, stack_att_split, stack_att_keys, M.attn_part, stream));
       kl += stack_att_split > 1 ? 3 : 2;
       if (par) {

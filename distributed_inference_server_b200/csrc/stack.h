@@ -102,7 +102,7 @@ cudaError_t launch_stack_attn_prep(const float *proj, long long ld, int q_off, i
                                    const float *kn, const double *freq, const double *vfreq, const StackAttn &c, const StackSpans &sp,
                                    float *qf, void *kpool, void *vpool, float *vrot, bool f32, const int *page_table, int max_pages,
                                    int page_size, cudaStream_t st);
-// query blocks hold at most stack_attn_block_tokens() tokens of one span; n_split > 1: slices of keys_per_split keys (a multiple
+// query blocks hold at most stack_attn_block_tokens() tokens of one span (bq: the most tokens a block of this pass holds); n_split > 1: slices of keys_per_split keys (a multiple
 // of 32), records of dv + 2 floats per (slice, token, head) in `part`, merged by a second kernel.  The result, times out_scale
 // and rotated back when values were rotated, lands in out [T][ld_out] (compute type) at columns out_off + h * dv.
 // bf16 with dim % 8 == 0, vdim % 16 == 0, both <= 128 and at most 64 query heads per key/value head: the mma.sync kernel (blocks
